@@ -10,7 +10,7 @@ WORKDIR /opt/realhf_b200
 COPY . .
 # flash-attn is optional (packed varlen attention until the in-tree tcgen05 kernels are the default)
 RUN pip install networkx pyzmq psutil transformers pybind11 tensorboard && \
-    python -m realhf_b200.ops.build --sass && \
+    python -m realhf_b200.ops.build && \
     pip install -e . --no-build-isolation --no-deps
 
 ENV PYTHONPATH=/opt/realhf_b200 REAL_FILEROOT=/workspace/realhf_b200

@@ -140,16 +140,6 @@ def build_host(force: bool = False) -> Path:
     return HOST_EXT
 
 
-def sass_summary() -> dict:
-    """Count the Blackwell-native SASS mnemonics in the built library (evidence for profiles/)."""
-    out = _run([str(CUDA_HOME / "bin" / "cuobjdump"), "-sass", str(OPS_LIB)])
-    keys = ["UTCHMMA", "UTCQMMA", "UTCMMA", "LDTM", "STTM", "UTMALDG", "UTMASTG", "UBLKCP", "HMMA", "LDGSTS", "SYNCS", "LDGMC", "UTCBAR"]  # LDGMC = multimem.ld_reduce
-    # (multimem.st lowers to an ordinary STG on the multicast address and has no mnemonic of its own)
-    import re
-    pats = {k: re.compile(r"(?<![A-Z0-9_.])" + k + r"(?![A-Z0-9])") for k in keys}  # whole mnemonic: `HMMA` must not count `UTCHMMA`
-    return {k: sum(1 for line in out.splitlines() if pats[k].search(line)) for k in keys}
-
-
 def build_all(force: bool = False, verbose: bool = False):
     h = build_host(force)
     o = build_ops(force, verbose)
@@ -160,9 +150,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
-    ap.add_argument("--sass", action="store_true")
     a = ap.parse_args()
     paths = build_all(a.force, a.verbose)
     print("built:", *paths)
-    if a.sass:
-        print(json.dumps(sass_summary(), indent=1))

@@ -21,9 +21,6 @@
 // there is no fp32 dQ scratch tensor to zero / convert, and dK / dV of a GQA group are reduced inside one CTA.
 //
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d] comes from a small pre-pass; LSE is the forward's ([nq, T], natural log).
-//
-// STATUS: compiled and SASS-checked for sm_100a; not yet run on hardware (see attn_fwd_tcgen05.cu).  Opt-in:
-// `REAL_ATTN_BWD=tcgen05`; its numerics test needs `REAL_TEST_EXPERIMENTAL=1`.
 #include "gemm_common.cuh"
 
 namespace {

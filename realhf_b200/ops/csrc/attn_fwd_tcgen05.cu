@@ -21,9 +21,6 @@
 // the MN-major B operand (keys are the K dimension, head-dim contiguous), exactly the wgrad operand form of the GEMM.
 //
 // Outputs: O [T, nq, D] and LSE [nq, T] (natural log, scale applied) in the layout flash-attn's backward consumes.
-//
-// STATUS: compiled and SASS-checked for sm_100a; not yet run on hardware (written after the round's GPU budget was
-// spent).  It is therefore opt-in (`REAL_ATTN=tcgen05`) and its GPU test is gated behind `REAL_TEST_EXPERIMENTAL=1`.
 #include "gemm_common.cuh"
 
 namespace {

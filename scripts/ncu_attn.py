@@ -1,6 +1,6 @@
 """Tiny driver for ncu captures of the tcgen05 attention kernels: `python scripts/ncu_attn.py fwd|bwd [seqs] [len]`.
 
-    ncu --set full --clock-control none --import-source on -k regex:attn_fwd_kernel -c 1 -o gpurun_out/attn_fwd \
+    ncu --set full --clock-control none -k regex:attn_fwd_kernel -c 1 -o gpurun_out/attn_fwd \
         python scripts/ncu_attn.py fwd
     ncu -i gpurun_out/attn_fwd.ncu-rep --page raw --csv > profiles/ncu_attn_fwd_raw.csv      (read here, after the run)
 """

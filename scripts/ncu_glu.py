@@ -1,5 +1,5 @@
 """Driver for an ncu capture of the gate|up GEMM with the SwiGLU epilogue (LLaMA-7B shapes, 20480 tokens):
-    ncu --set full --clock-control none --import-source on -k regex:gemm_2cta_kernel -c 1 -o gpurun_out/gemm_glu python scripts/ncu_glu.py
+    ncu --set full --clock-control none -k regex:gemm_2cta_kernel -c 1 -o gpurun_out/gemm_glu python scripts/ncu_glu.py
 """
 import os
 import sys
