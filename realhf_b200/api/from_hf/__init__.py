@@ -292,3 +292,5 @@ register_hf_family(
         n_layers=4, n_kv_heads=8, n_q_heads=8, hidden_dim=64, intermediate_dim=256, vocab_size=128, n_positions=512,
         embd_pdrop=0.0, resid_pdrop=0.0, attn_pdrop=0.0, activation_function="gelu_new",
         scale_attn_by_inverse_layer_idx=False, tied_embedding=True))
+
+from realhf_b200.api.from_hf import rapodra  # noqa: E402,F401  (registers the family)

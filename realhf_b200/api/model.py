@@ -61,6 +61,48 @@ class ReaLMoEConfig:
 
 
 @dataclasses.dataclass
+class LatentAttentionConfig:
+    """Attention whose keys and values are up-projections of one shared low-rank latent per token (only the latent is cached),
+    without positional rotation.  `window`: a query at position i sees positions (i - window, i]; None = the whole prefix.
+    `kv_from`: 0-based index of an EARLIER block whose cached latent this block reads instead of projecting its own."""
+    n_heads: int
+    qk_dim: int
+    v_dim: int
+    kv_rank: int
+    scale: float
+    window: Optional[int] = None
+    kv_from: Optional[int] = None
+
+
+@dataclasses.dataclass
+class BlockMLPConfig:
+    """Feed-forward of one block of a heterogeneous stack.  kind `clamped_glu`: y = g * sigmoid(alpha g) * (u + 1) with
+    g = min(gate, limit), u = clamp(up, -limit, limit); kind `moe`: `moe.num_experts` SiLU-gated experts of width `ff`, the
+    `moe.top_k` largest router logits (with a router bias) are chosen and weighted by the softmax over the chosen logits."""
+    kind: str                      # clamped_glu | moe
+    ff: int
+    limit: float = 0.0
+    alpha: float = 1.702
+    moe: Optional[ReaLMoEConfig] = None
+
+
+@dataclasses.dataclass
+class BlockConfig:
+    """One entry of `ReaLModelConfig.blocks` (a stack whose blocks differ from each other)."""
+    mixer: str                     # latent_attention
+    attn: Optional[LatentAttentionConfig] = None
+    mlp: Optional[BlockMLPConfig] = None   # None: the block has no feed-forward sublayer
+
+    def __post_init__(self):
+        if isinstance(self.attn, dict):
+            self.attn = LatentAttentionConfig(**self.attn)
+        if isinstance(self.mlp, dict):
+            self.mlp = BlockMLPConfig(**self.mlp)
+        if self.mlp is not None and isinstance(self.mlp.moe, dict):
+            self.mlp.moe = ReaLMoEConfig(**self.mlp.moe)
+
+
+@dataclasses.dataclass
 class ReaLModelConfig:
     n_layers: int
     n_kv_heads: int
@@ -94,10 +136,30 @@ class ReaLModelConfig:
     sliding_window: Optional[int] = None
     moe: Optional[ReaLMoEConfig] = None
     is_critic: bool = False
+    # ---- heterogeneous stacks (B200 addition, no reference counterpart): `blocks[i]` describes block i + 1; the homogeneous fields
+    # above (heads, intermediate_dim, mlp_type, ...) are then only summaries.  The remaining fields are mechanisms any family may use.
+    blocks: Optional[List[BlockConfig]] = None
+    norm_groups: int = 1                 # RMSNorm in `norm_groups` equal consecutive parts, each with its own root mean square
+    sandwich_norm: bool = False          # a second norm on every sublayer's OUTPUT, before the residual add
+    conv_taps: int = 0                   # h <- h + causal depthwise conv(h) over time on every sublayer's input (0 = none);
+                                         # the last conv_taps - 1 inputs are part of a sequence's decode state
+    logit_softcap: Optional[float] = None  # logits <- cap * tanh(logits / cap)
+    fp32_residual: bool = False          # the residual stream is kept in fp32 whatever the compute dtype
 
     def __post_init__(self):
         if self.is_critic and self.tied_embedding:
             raise ValueError("a critic cannot tie its embedding and output weights")
+        if self.blocks is not None:
+            self.blocks = [BlockConfig(**b) if isinstance(b, dict) else b for b in self.blocks]
+            if len(self.blocks) != self.n_layers:
+                raise ValueError("`blocks` must describe every layer")
+            for i, b in enumerate(self.blocks):
+                if b.mixer != "latent_attention":
+                    raise ValueError(f"block {i}: unknown mixer `{b.mixer}`")
+                src = b.attn.kv_from
+                if src is not None and not (0 <= src < i and self.blocks[src].attn.kv_from is None
+                                            and self.blocks[src].attn.kv_rank == b.attn.kv_rank):
+                    raise ValueError(f"block {i}: kv_from must name an earlier block that projects a latent of the same rank")
         if self.head_dim is None:
             self.head_dim = self.hidden_dim // self.n_q_heads
         if isinstance(self.moe, dict):
@@ -106,6 +168,16 @@ class ReaLModelConfig:
     def n_params(self) -> int:
         """Parameter count (used by the PP partitioner, the FLOP model and the allocation search)."""
         h, f, v = self.hidden_dim, self.intermediate_dim, self.vocab_size
+        if self.blocks is not None:
+            n = 2 * v * h + h
+            for b in self.blocks:
+                a = b.attn
+                n += h * a.n_heads * a.qk_dim + (h * a.kv_rank + a.kv_rank if a.kv_from is None else 0)
+                n += a.kv_rank * a.n_heads * (a.qk_dim + a.v_dim) + a.n_heads * a.v_dim * h + (2 + self.conv_taps) * h
+                if b.mlp is not None:
+                    e = b.mlp.moe.num_experts if b.mlp.kind == "moe" else 1
+                    n += e * 3 * h * b.mlp.ff + (e * (h + 1) if b.mlp.kind == "moe" else 0) + (2 + self.conv_taps) * h
+            return n
         qkv = h * self.head_dim * (self.n_q_heads + 2 * self.n_kv_heads)
         attn = qkv + self.n_q_heads * self.head_dim * h
         if self.mlp_type == "moe":
@@ -338,14 +410,19 @@ class HFFamilySpec:
     head_param_names: Callable[[ReaLModelConfig], List[str]]
     make_test_config: Optional[Callable[[], ReaLModelConfig]] = None
     real_config_maker: Optional[Callable] = None
+    # families without a `transformers` class: `config.json` is read and written as a plain dict, and all weights live in one file
+    config_from_dict: Optional[Callable[[dict, bool], ReaLModelConfig]] = None
+    config_to_dict: Optional[Callable[[ReaLModelConfig], dict]] = None
+    weight_file: Optional[str] = None
 
 
 def register_hf_family(name: str, hf_cls_name: str, config_from_hf_converter, config_to_hf_converter,
                        sd_from_hf_converter, sd_to_hf_converter, embedding_param_names, tblock_param_names,
-                       head_param_names, real_config_maker=None, make_test_config=None):
+                       head_param_names, real_config_maker=None, make_test_config=None, config_from_dict=None, config_to_dict=None,
+                       weight_file=None):
     if name in SUPPORTED_HF_FAMILIES:
         raise KeyError(f"HF family `{name}` already registered")
     SUPPORTED_HF_FAMILIES[name] = HFFamilySpec(name, hf_cls_name, config_from_hf_converter, config_to_hf_converter,
                                                sd_from_hf_converter, sd_to_hf_converter, embedding_param_names,
                                                tblock_param_names, head_param_names, make_test_config,
-                                               real_config_maker)
+                                               real_config_maker, config_from_dict, config_to_dict, weight_file)

@@ -111,9 +111,26 @@ class DecodeState:
         nq, nkv = model._local_heads()
         dev, dt = model.device, model.dtype
         nb = model.n_local_blocks()
-        # [B, nkv, S, hd] storage viewed as logical [B, S, nkv, hd]
-        self.k = [torch.zeros(B, nkv, S, c.head_dim, dtype=dt, device=dev).permute(0, 2, 1, 3) for _ in range(nb)]
-        self.v = [torch.zeros(B, nkv, S, c.head_dim, dtype=dt, device=dev).permute(0, 2, 1, 3) for _ in range(nb)]
+        self.hetero = c.blocks is not None
+        if self.hetero:
+            # per block: the latent ring [B, R, rank] (a block that reads another block's latent holds that block's tensor) and
+            # the convolution state [2, B, taps - 1, H] fp32 (mixer / feed-forward inputs); see models/hetero_block.py
+            from realhf_b200.models import hetero_block as HB
+            first = model.layers[0] if model.layers[0] >= 1 else 1
+            self.k, self.v = [], []
+            for i in (j for j in model.layers if 1 <= j <= c.n_layers):
+                a = c.blocks[i - 1].attn
+                if a.kv_from is None:
+                    self.k.append(torch.zeros(B, HB.ring_rows(c, i - 1, S), a.kv_rank, dtype=dt, device=dev))
+                else:
+                    assert a.kv_from + 1 >= first, "a block and the block whose latent it reads must share a pipeline stage"
+                    self.k.append(self.k[a.kv_from + 1 - first])
+                self.v.append(torch.zeros(2, B, max(c.conv_taps - 1, 0), c.hidden_dim, dtype=torch.float32, device=dev))
+        else:
+            # [B, nkv, S, hd] storage viewed as logical [B, S, nkv, hd]
+            self.k = [torch.zeros(B, nkv, S, c.head_dim, dtype=dt, device=dev).permute(0, 2, 1, 3) for _ in range(nb)]
+            self.v = [torch.zeros(B, nkv, S, c.head_dim, dtype=dt, device=dev).permute(0, 2, 1, 3) for _ in range(nb)]
+        self.free_slots: List[int] = list(range(B))
         self.cache_lens = torch.zeros(B, dtype=torch.int32, device=dev)
         self.input_ids = torch.zeros(B, dtype=torch.long, device=dev)
         self.hidden_in = torch.zeros(B, c.hidden_dim, dtype=dt, device=dev) if not model.is_first_stage else None
@@ -128,6 +145,26 @@ class DecodeState:
         self.unfinished = torch.ones(B, dtype=torch.bool, device=dev)
         self.seed = torch.zeros(1, dtype=torch.long, device=dev)
         self.tok_hist = self.lp_hist = self.mask_hist = None
+
+    # ---- slot manager: a slot is one row of every state tensor
+    def alloc(self, n: int) -> List[int]:
+        """Take n free slots (lowest first) and reset their state: length 0, convolution history zero."""
+        if n > len(self.free_slots):
+            raise RuntimeError(f"decode state has {len(self.free_slots)} free slots, {n} requested")
+        self.free_slots.sort()
+        got, self.free_slots = self.free_slots[:n], self.free_slots[n:]
+        idx = torch.tensor(got, dtype=torch.long, device=self.cache_lens.device)
+        self.cache_lens[idx] = 0
+        if self.hetero:
+            for v in self.v:
+                if v.shape[2]:
+                    v[:, idx] = 0
+        return got
+
+    def release(self, slots: List[int]):
+        for s_ in slots:
+            assert s_ not in self.free_slots
+            self.free_slots.append(int(s_))
 
     def prepare_hist(self, n_gen: int, V: int, need_mask: bool):
         dev = self.cache_lens.device
@@ -161,7 +198,100 @@ def _final_logits(model: ReaLModel, hidden: torch.Tensor) -> torch.Tensor:
     lg = OF.linear(hidden, model.head_weight())
     if model.ctx.tp_size > 1:
         lg = TP._gather_last_dim(lg, model.ctx)
+    if model.config.logit_softcap is not None:
+        lg = OF.softcap_logits(lg, model.config.logit_softcap)
     return lg
+
+
+@torch.no_grad()
+def prefill_into_state(model: ReaLModel, state: DecodeState, slots: List[int], input_ids: torch.Tensor, cu: torch.Tensor,
+                       max_seqlen: Optional[int] = None) -> torch.Tensor:
+    """Packed prefill of len(slots) sequences whose decode state goes to `slots` of `state`.  Returns the final hidden states of
+    all packed tokens [T, H].  One code path for `generate`, the in-flight batcher and the step session."""
+    cu = cu.int()
+    lens = cu[1:] - cu[:-1]
+    idx = torch.tensor(slots, dtype=torch.long, device=cu.device)
+    if max_seqlen is None:
+        max_seqlen = int(lens.max())
+    if state.hetero:
+        out = model(input_ids=input_ids, cu_seqlens=cu, max_seqlen=max_seqlen, kv_sink=(state, idx.int()))
+    else:
+        kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
+        out = model(input_ids=input_ids, cu_seqlens=cu, max_seqlen=max_seqlen, kv_sink=kv)
+        tok = torch.arange(int(input_ids.shape[0]), device=cu.device)
+        seq = torch.searchsorted(cu[1:].long().contiguous(), tok, right=True)
+        pos = tok - cu.long()[seq]
+        for li, (k, v) in enumerate(kv):
+            state.k[li][idx[seq], pos] = k
+            state.v[li][idx[seq], pos] = v
+    state.cache_lens[idx] = lens
+    return out.hidden
+
+
+class StepSession:
+    """Step-wise serving on one `DecodeState`: requests enter by a packed prefill into free slots, go on one token per step in
+    any sub-batch, and give their slots back when they end.  The logits of any processed token can be asked for.  This is the
+    generation path (`prefill_into_state`, `ReaLModel.decode_step`, `_final_logits`) without the sampler: the caller feeds the
+    tokens.  The state grows (keeping live slots) when a step needs more slots than are free."""
+
+    def __init__(self, model: ReaLModel, max_len: int, n_slots: int = 4):
+        assert model.is_first_stage and model.is_last_stage and model.config.blocks is not None
+        self.model, self.max_len = model, int(max_len)
+        model.eval()
+        self.state = DecodeState(model, n_slots, self.max_len)
+        self.state.free_slots = list(range(n_slots))
+        self.slot_of: dict = {}
+
+    def _grow(self, n_needed: int):
+        old = self.state
+        B = max(2 * old.B, old.B + n_needed - len(old.free_slots))
+        new = DecodeState(self.model, B, self.max_len)
+        done = set()
+        for a, b_ in zip(old.k + old.v + [old.cache_lens], new.k + new.v + [new.cache_lens]):
+            if id(a) in done:
+                continue
+            done.add(id(a))
+            if a.dim() == 4:          # [2, B, taps - 1, H]
+                b_[:, : old.B] = a
+            else:
+                b_[: old.B] = a
+        new.free_slots = old.free_slots + list(range(old.B, B))
+        self.state = new
+
+    @torch.no_grad()
+    def prefill(self, requests: List[Tuple[object, List[int]]]) -> torch.Tensor:
+        """requests: (id, tokens) of NEW requests.  Returns the hidden states of all their tokens, packed in order [T, H]."""
+        assert all(r not in self.slot_of for r, _ in requests) and all(len(t) > 0 for _, t in requests)
+        if max(len(t) for _, t in requests) > self.max_len:
+            raise RuntimeError("a request is longer than the session's max_len")
+        if len(requests) > len(self.state.free_slots):
+            self._grow(len(requests))
+        slots = self.state.alloc(len(requests))
+        for (r, _), s_ in zip(requests, slots):
+            self.slot_of[r] = s_
+        dev = self.model.device
+        lens = [len(t) for _, t in requests]
+        ids = torch.tensor([x for _, t in requests for x in t], dtype=torch.long, device=dev)
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int32, device=dev)
+        cu[1:] = torch.tensor(lens, dtype=torch.int32, device=dev).cumsum(0)
+        return prefill_into_state(self.model, self.state, slots, ids, cu, max(lens))
+
+    @torch.no_grad()
+    def decode(self, requests: List[Tuple[object, int]]) -> torch.Tensor:
+        """requests: (id, next token) of live requests.  Returns their final hidden states [b, H] in order."""
+        dev = self.model.device
+        slots = torch.tensor([self.slot_of[r] for r, _ in requests], dtype=torch.int32, device=dev)
+        ids = torch.tensor([t for _, t in requests], dtype=torch.long, device=dev)
+        st = self.state
+        h = self.model.decode_step(ids, st.k, st.v, st.cache_lens, slots=slots)
+        st.cache_lens[slots.long()] += 1
+        return h
+
+    def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
+        return _final_logits(self.model, hidden_rows).float()
+
+    def release(self, ids: List[object]):
+        self.state.release([self.slot_of.pop(r) for r in ids])
 
 
 @torch.no_grad()
@@ -194,14 +324,13 @@ def generate(model: ReaLModel, input_ids: torch.Tensor, cu_seqlens: torch.Tensor
             marks.append((name, e))
     mark("start")
     # ---- prefill
-    kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
-    out = model(input_ids=input_ids, cu_seqlens=cu, max_seqlen=max_prompt, kv_sink=kv)
-    last = (cu[1:] - 1).long()
-    logits = _final_logits(model, out.hidden.index_select(0, last))
     if state is None or state.B != B or state.S < S:
         state = DecodeState(model, B, S)
-    state.fill_from_prefill(kv, cu, lens)
-    del kv, out
+    state.free_slots = list(range(B))
+    hidden = prefill_into_state(model, state, state.alloc(B), input_ids, cu, max_prompt)
+    last = (cu[1:] - 1).long()
+    logits = _final_logits(model, hidden.index_select(0, last))
+    del hidden
     unfinished = torch.ones(B, dtype=torch.bool, device=dev)
     toks, lps, masks = [], [], []
     nxt, lp, mb, unfinished = genstep(logits, g, 0, eos_id, pad_id, unfinished, generator)
@@ -379,14 +508,9 @@ class InflightBatchingGenerator:
     def _refill(self, slot: int, req_id: int, prompt: torch.Tensor):
         m, st = self.model, self.state
         cu = torch.tensor([0, prompt.numel()], dtype=torch.int32, device=m.device)
-        kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
-        out = m(input_ids=prompt, cu_seqlens=cu, max_seqlen=int(prompt.numel()), kv_sink=kv)
-        logits = _final_logits(m, out.hidden[-1:])
-        n = prompt.numel()
-        for li, (k, v) in enumerate(kv):
-            st.k[li][slot, :n] = k
-            st.v[li][slot, :n] = v
-        st.cache_lens[slot] = n
+        st.free_slots = [slot]
+        hidden = prefill_into_state(m, st, st.alloc(1), prompt, cu, int(prompt.numel()))
+        logits = _final_logits(m, hidden[-1:])
         one = torch.ones(1, dtype=torch.bool, device=m.device)
         nxt, lp, _, _ = genstep(logits, self.g, 0, self.eos_id, self.pad_id, one, want_mask=False)
         st.input_ids[slot] = nxt[0]

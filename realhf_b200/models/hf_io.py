@@ -62,12 +62,30 @@ def config_from_hf_path(family_name: str, path: str, is_critic: bool = False) ->
     config that produced the weights): reading it avoids instantiating the HuggingFace config class, whose first import costs
     every worker process several seconds (`transformers` pulls `torch._dynamo` in).  `REAL_TRUST_SAVED_MODEL_CONFIG=0` always goes
     through `config.json`; so do foreign checkpoints and a critic initialised from an actor checkpoint."""
+    fam = family(family_name)
+    if fam.config_from_dict is not None:
+        with open(os.path.join(path, "config.json")) as f:
+            return fam.config_from_dict(json.load(f), is_critic)
     fast = os.path.join(path, "real_model_config.json")
     if os.environ.get("REAL_TRUST_SAVED_MODEL_CONFIG", "1") == "1" and os.path.exists(fast):
         cfg = _config_from_saved_json(fast, family_name, is_critic)
         if cfg is not None:
             return cfg
     return family(family_name).config_from_hf(load_hf_config(path), is_critic)
+
+
+def family_of_path(path: str) -> str:
+    """The registered family a checkpoint directory belongs to, decided by its `config.json` alone: the `architecture` /
+    `architectures` / `model_type` entry is matched against the families' class names and registry names."""
+    import realhf_b200.api.from_hf  # noqa: F401
+    with open(os.path.join(path, "config.json")) as f:
+        d = json.load(f)
+    tags = [d.get("architecture")] + list(d.get("architectures") or []) + [d.get("model_type")]
+    tags = [str(t).lower() for t in tags if t]
+    for name, fam in SUPPORTED_HF_FAMILIES.items():
+        if any(t in (name.lower(), fam.hf_cls_name.lower()) for t in tags):
+            return name
+    raise KeyError(f"{path}/config.json names no registered model family (saw {tags})")
 
 
 # ------------------------------------------------------------------------------------------- reading
@@ -203,9 +221,13 @@ def save_to_hf(model: ReaLModel, family_name: str, save_dir: str, tokenizer=None
         weight_map = {k: fn for files in maps for fn, keys in files for k in keys}
         with open(os.path.join(save_dir, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {}, "weight_map": weight_map}, f, indent=1)
-        hf_cfg = fam.config_to_hf(cfg)
-        hf_cfg.architectures = [fam.hf_cls_name]
-        hf_cfg.save_pretrained(save_dir)
+        if fam.config_to_dict is not None:
+            with open(os.path.join(save_dir, "config.json"), "w") as f:
+                json.dump(fam.config_to_dict(cfg), f, indent=1)
+        else:
+            hf_cfg = fam.config_to_hf(cfg)
+            hf_cfg.architectures = [fam.hf_cls_name]
+            hf_cfg.save_pretrained(save_dir)
         with open(os.path.join(save_dir, "real_model_config.json"), "w") as f:
             import dataclasses
             json.dump(dict(dataclasses.asdict(cfg), _family=family_name), f, indent=1)

@@ -10,7 +10,7 @@ ranks and tokens travel by all-to-all (`dispatch -> grouped GEMM -> combine`); t
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -42,11 +42,11 @@ def sinkhorn(cost: torch.Tensor, tol: float = 1e-4, max_iter: int = 100) -> torc
     return d1 * cost * d0.unsqueeze(1)
 
 
-def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool) -> Tuple[torch.Tensor, torch.Tensor]:
-    """h [T,H] -> (probs [T,k] fp32 normalised over the chosen experts, expert ids [T,k])."""
+def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool, bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """h [T,H] -> (probs [T,k] fp32 normalised over the chosen experts, expert ids [T,k]).  Logits (+ `bias`) are fp32."""
     if training and mcfg.input_jitter_eps > 0:
         h = h * torch.empty_like(h).uniform_(1 - mcfg.input_jitter_eps, 1 + mcfg.input_jitter_eps)
-    logits = F.linear(h.float(), w_router.float())
+    logits = F.linear(h.float(), w_router.float(), bias.float() if bias is not None else None)
     if training and mcfg.z_loss_coeff > 0:
         MOE_STATS["z_loss"].append(torch.logsumexp(logits, -1).square().mean() * mcfg.z_loss_coeff)
     if mcfg.routing_type == "sinkhorn" and training:
@@ -54,6 +54,9 @@ def route(h: torch.Tensor, w_router: torch.Tensor, mcfg, training: bool) -> Tupl
             _, idx = torch.topk(sinkhorn(logits), mcfg.top_k, dim=-1)
         probs = torch.sigmoid(logits).gather(-1, idx) if mcfg.top_k == 1 else torch.softmax(logits, -1).gather(-1, idx)
         return probs, idx
+    if mcfg.routing_type == "none":  # the k largest logits, weighted by the softmax over those k alone
+        top, idx = torch.topk(logits, mcfg.top_k, dim=-1)
+        return torch.softmax(top, dim=-1), idx
     full = torch.softmax(logits, dim=-1)
     probs, idx = torch.topk(full, mcfg.top_k, dim=-1)
     probs = probs / probs.sum(-1, keepdim=True)
@@ -122,10 +125,12 @@ def grouped_mlp(x_sorted: torch.Tensor, counts: List[int], w_gate_up: torch.Tens
     return torch.cat(outs, 0)
 
 
-def moe_forward(model, i: int, h: torch.Tensor) -> torch.Tensor:
-    """MoE MLP of block i on normalised hidden states h ([T, H], or [T/t, H] under sequence parallelism)."""
+def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
+    """MoE MLP of block i on normalised hidden states h ([T, H], or [T/t, H] under sequence parallelism).  `mcfg`: the block's own
+    MoE config in a heterogeneous stack (default: the model-wide one).  With `fp32_residual` the experts' outputs are combined
+    in fp32 and the result stays fp32."""
     c, ctx = model.config, model.ctx
-    mcfg = c.moe
+    mcfg = mcfg if mcfg is not None else c.moe
     E, k = mcfg.num_experts, mcfg.top_k
     w_gu, w_dn = model.p[f"{i}.mlp.experts.gate_up.weight"], model.p[f"{i}.mlp.experts.down.weight"]
     ep = mcfg.expert_parallel and ctx.tp_size > 1
@@ -137,7 +142,7 @@ def moe_forward(model, i: int, h: torch.Tensor) -> torch.Tensor:
     else:
         h = TP.copy_to_tp(h, ctx)
     T, H = h.shape
-    probs, idx = route(h, model.p[f"{i}.mlp.router.weight"], mcfg, model.training)
+    probs, idx = route(h, model.p[f"{i}.mlp.router.weight"], mcfg, model.training, model.p.get(f"{i}.mlp.router.bias"))
     probs = _apply_capacity(probs, idx, E, mcfg)
     flat_e = idx.reshape(-1)
     order = torch.argsort(flat_e, stable=True)
@@ -196,7 +201,10 @@ def moe_forward(model, i: int, h: torch.Tensor) -> torch.Tensor:
     else:
         counts = torch.bincount(flat_e, minlength=E).tolist()
         y_sorted = grouped_mlp(x_sorted, counts, w_gu, w_dn, c.activation_function)
-    out = torch.zeros(T, H, dtype=y_sorted.dtype, device=h.device).index_add_(0, tok, y_sorted * w_sorted.to(y_sorted.dtype).unsqueeze(-1))
+    if c.fp32_residual:
+        out = torch.zeros(T, H, dtype=torch.float32, device=h.device).index_add_(0, tok, y_sorted.float() * w_sorted.unsqueeze(-1))
+    else:
+        out = torch.zeros(T, H, dtype=y_sorted.dtype, device=h.device).index_add_(0, tok, y_sorted * w_sorted.to(y_sorted.dtype).unsqueeze(-1))
     if ctx.tp_size > 1:  # experts are F-sharded over TP: partial sums
         out = TP.reduce_scatter_to_sp(out, ctx) if sp else TP.reduce_from_tp(out, ctx)
     return out

@@ -77,6 +77,7 @@ class ModelOutput:
     ctx: Optional[ParallelContext]
     is_critic: bool = False
     _logits: Optional[torch.Tensor] = None
+    softcap: Optional[float] = None      # models with a soft cap on the logits: `logits` are the capped fp32 values
 
     @property
     def logits(self) -> torch.Tensor:
@@ -87,6 +88,8 @@ class ModelOutput:
                 tp = self.ctx is not None and self.ctx.tp_size > 1
                 lg = OF.linear(TP.copy_to_tp(self.hidden, self.ctx) if tp else self.hidden, self.head_weight)
                 self._logits = TP.gather_last_dim(lg, self.ctx) if tp else lg
+                if self.softcap is not None:
+                    self._logits = OF.softcap_logits(self._logits, self.softcap)
         return self._logits
 
     @property
@@ -98,6 +101,9 @@ class ModelOutput:
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """fp32 log p(labels[i] | hidden[rows[i]]) (rows defaults to all tokens)."""
         h = self.hidden if rows is None else self.hidden.index_select(0, rows)
+        if self.softcap is not None:  # the fused LM-head + log-prob kernel has no cap stage: capped logits are materialised
+            lg = OF.softcap_logits(OF.linear(h, self.head_weight), self.softcap)
+            return OF.logprob_from_logits(lg, labels, mask_bits, 1.0 / temperature)[0]
         if self.ctx is not None and self.ctx.tp_size > 1:
             local = OF.linear(TP.copy_to_tp(h, self.ctx), self.head_weight)  # column-parallel head: d(hidden) is summed over TP
             return TP.vocab_parallel_logprobs(local, labels, self.ctx, temperature, mask_bits)
@@ -114,6 +120,8 @@ class ReaLModel(nn.Module):
             raise NotImplementedError("do_layernorm_before=False (post-LN blocks) is not supported")
         self.config = config
         self.ctx = ctx if ctx is not None else ParallelContext.single()
+        if config.blocks is not None and self.ctx.tp_size > 1:
+            raise NotImplementedError("heterogeneous stacks (`config.blocks`) are not tensor-parallel")
         self.dtype = dtype
         self.device = torch.device(device)
         if layer_range is None:
@@ -338,13 +346,15 @@ class ReaLModel(nn.Module):
     def _embed(self, input_ids, position_ids):
         c = self.config
         x = TP.vocab_parallel_embedding(input_ids, self.p["0.wte.weight"], self.ctx, sp=self.sequence_parallel)
-        if not c.apply_rotary:
+        if not c.apply_rotary and c.n_positions:
             pe = F.embedding(position_ids.long() + c.abs_position_embedding_offset, self.p["0.wpe.weight"])
             if self.sequence_parallel:
                 pe = TP._split_first_dim(pe, self.ctx)
             x = x + pe
         if c.normalize_embed:
             x = x * torch.tensor(c.hidden_dim ** 0.5, dtype=x.dtype, device=x.device)
+        if c.fp32_residual:
+            x = x.float()
         return self._dropout(x, c.embd_pdrop)
 
     # ------------------------------------------------------------------ dropout under tensor parallelism
@@ -527,11 +537,16 @@ class ReaLModel(nn.Module):
         First stage: `input_ids` [T]; later stages: `hidden` [T(/tp), H].  cu_seqlens: int32 [B+1].
         With sequence parallelism the caller (engine) has padded T to a multiple of tp.
         Returns a ModelOutput on the last stage, else the hidden-state tensor for the next stage.
+
+        `kv_sink`: a list that receives every block's packed (K, V) for the caller to scatter into its cache; for heterogeneous
+        stacks a `(DecodeState, slots)` pair instead, and the blocks write each sequence's state straight into its slot.
         """
         c = self.config
         if self.flat_param is None and self._offloaded is not None:
             self.reload()  # offloaded by an OffloadHook after its last call: bring the weights back on first use
         cu_seqlens = cu_seqlens.int()
+        if c.blocks is not None:
+            return self._forward_hetero(input_ids, cu_seqlens, hidden, kv_sink)
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         T = int(input_ids.shape[0]) if input_ids is not None else None
@@ -569,6 +584,29 @@ class ReaLModel(nn.Module):
             x = TP.gather_from_sp(x, self.ctx, reduce_scatter_bwd=False)
         return ModelOutput(hidden=x, head_weight=self.head_weight(), ctx=self.ctx, is_critic=c.is_critic)
 
+    def _forward_hetero(self, input_ids, cu_seqlens, hidden, kv_sink):
+        """Packed forward of a heterogeneous stack (inference only: its kernels have no backward)."""
+        from realhf_b200.models import hetero_block as HB
+        c = self.config
+        assert not torch.is_grad_enabled() or not any(p.requires_grad for p in self.p.values()), \
+            "heterogeneous stacks are inference-only"
+        T = int(input_ids.shape[0]) if input_ids is not None else int(hidden.shape[0])
+        state, slots = kv_sink if kv_sink is not None else (None, None)
+        meta = HB.packed_meta(cu_seqlens, T, slots, state)
+        x, li = hidden, 0
+        with torch.no_grad():
+            for i in self.layers:
+                if i == 0:
+                    x = self._embed(input_ids, meta.pos)
+                elif i <= c.n_layers:
+                    x = HB.block_packed(self, i, li, x, meta)
+                    li += 1
+                    if i == c.n_layers:
+                        x = HB.final_norm(self, x)
+        if not self.is_last_stage:
+            return x
+        return ModelOutput(hidden=x, head_weight=self.head_weight(), ctx=self.ctx, is_critic=c.is_critic, softcap=c.logit_softcap)
+
     def _n_unckpt_blocks(self, n_tokens: int) -> int:
         """How many transformer blocks of this forward pass may keep their activations instead of being recomputed.
 
@@ -594,10 +632,25 @@ class ReaLModel(nn.Module):
     # ------------------------------------------------------------------ decode step (one token per sequence)
     @torch.no_grad()
     def decode_step(self, input_ids: Optional[torch.Tensor], k_caches: List[torch.Tensor], v_caches: List[torch.Tensor],
-                    cache_lens: torch.Tensor, hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    cache_lens: torch.Tensor, hidden: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> torch.Tensor:
         """input_ids [B] -> final hidden [B, H] (last stage: after ln_f).  Appends K/V at `cache_lens` in place.
-        Caches: one [B, S, nkv_local, hd] tensor per local block.  Capturable in a CUDA graph (no host sync)."""
+        Caches: one [B, S, nkv_local, hd] tensor per local block.  Capturable in a CUDA graph (no host sync).
+        Heterogeneous stacks: the caches are the per-block state tensors of `DecodeState` (see models/hetero_block.py) and
+        `slots` [B] int32 names the state slot of every row (None: row b is slot b; `cache_lens` is indexed by slot)."""
         c = self.config
+        if c.blocks is not None:
+            from realhf_b200.models import hetero_block as HB
+            x, li = hidden, 0
+            for i in self.layers:
+                if i == 0:
+                    x = self._embed(input_ids, None)
+                elif i <= c.n_layers:
+                    x = HB.block_decode(self, i, li, x, k_caches, v_caches, cache_lens, slots)
+                    li += 1
+                    if i == c.n_layers:
+                        x = HB.final_norm(self, x)
+            return x
+        assert slots is None, "slot indirection is a feature of heterogeneous stacks"
         nq, nkv = self._local_heads()
         hd = c.head_dim
         x = hidden

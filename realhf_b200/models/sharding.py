@@ -44,7 +44,7 @@ def layer_param_specs(cfg: ReaLModelConfig, layer_idx: int, tied_head_copy: bool
     out: List[ParamSpec] = []
     if layer_idx == 0:
         out.append(P("wte.weight", (cfg.vocab_size, H), 0))
-        if not cfg.apply_rotary:
+        if not cfg.apply_rotary and cfg.n_positions:   # neither rotary nor a position table: a position-free stack
             out.append(P("wpe.weight", (cfg.n_positions, H), None))
         return out
     if layer_idx == L + 1:
@@ -59,6 +59,8 @@ def layer_param_specs(cfg: ReaLModelConfig, layer_idx: int, tied_head_copy: bool
         if ln_bias:
             out.append(P(f"{prefix}.bias", (H,), None, init="zeros", sp_grad_sync=True))
 
+    if cfg.blocks is not None:
+        return _hetero_block_specs(cfg, layer_idx, P)
     norm("attn.ln")
     qkv_sec = (nq * hd, nkv * hd, nkv * hd)
     out.append(P("attn.qkv.weight", (sum(qkv_sec), H), 0, qkv_sec, (1, 2)))
@@ -89,6 +91,52 @@ def layer_param_specs(cfg: ReaLModelConfig, layer_idx: int, tied_head_copy: bool
             out.append(P("mlp.proj.bias", (H,), None, init="zeros"))
     if layer_idx == L:
         norm("ln_f")
+    return out
+
+
+def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSpec]:
+    """Specs of block `layer_idx` of a heterogeneous stack (`cfg.blocks`).  Projections that read the same input are one tensor
+    made of sections: `attn.q_dkv` = [queries | latent down-projection] (the second section is absent in a block that reads
+    another block's latent), `attn.ukv` = [key up-projection | value up-projection], `mlp.gate_up` = [gate | up].  These
+    stacks are not tensor-parallel: every tensor is replicated."""
+    H = cfg.hidden_dim
+    b = cfg.blocks[layer_idx - 1]
+    a = b.attn
+    out: List[ParamSpec] = []
+
+    def add(*args, **kw):
+        out.append(P(*args, **kw))
+    add("attn.ln.weight", (H,), None, init="ones")
+    if cfg.conv_taps:
+        add("attn.canon.weight", (H, cfg.conv_taps), None)
+    own = a.kv_from is None
+    q_sec = (a.n_heads * a.qk_dim,) + ((a.kv_rank,) if own else ())
+    add("attn.q_dkv.weight", (sum(q_sec), H), None, q_sec)
+    if own:
+        add("attn.dkv_ln.weight", (a.kv_rank,), None, init="ones")
+    kv_sec = (a.n_heads * a.qk_dim, a.n_heads * a.v_dim)
+    add("attn.ukv.weight", (sum(kv_sec), a.kv_rank), None, kv_sec)
+    add("attn.o.weight", (H, a.n_heads * a.v_dim), None)
+    if cfg.sandwich_norm:
+        add("attn.ln_post.weight", (H,), None, init="ones")
+    if b.mlp is not None:
+        F = b.mlp.ff
+        add("mlp.ln.weight", (H,), None, init="ones")
+        if cfg.conv_taps:
+            add("mlp.canon.weight", (H, cfg.conv_taps), None)
+        if b.mlp.kind == "moe":
+            E = b.mlp.moe.num_experts
+            add("mlp.router.weight", (E, H), None)
+            add("mlp.router.bias", (E,), None, init="zeros")
+            add("mlp.experts.gate_up.weight", (E, 2 * F, H), None)
+            add("mlp.experts.down.weight", (E, H, F), None)
+        else:
+            add("mlp.gate_up.weight", (2 * F, H), None, (F, F))
+            add("mlp.down.weight", (H, F), None)
+        if cfg.sandwich_norm:
+            add("mlp.ln_post.weight", (H,), None, init="ones")
+    if layer_idx == cfg.n_layers:
+        add("ln_f.weight", (H,), None, init="ones")
     return out
 
 

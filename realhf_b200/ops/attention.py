@@ -180,3 +180,88 @@ def decode_attention(qkv, k_cache, v_cache, cache_lens, n_q: int, n_kv: int, hd:
     k_cache[idx, pos] = k.to(k_cache.dtype)
     v_cache[idx, pos] = v.to(v_cache.dtype)
     return decode_attention_ref(q, k_cache, v_cache, cache_lens + 1, scale).reshape(B, n_q * hd)
+
+
+# ------------------------------------------------------------------------------------------------ latent attention
+# Keys and values are up-projections of one cached low-rank latent per token; no positional rotation; optional sliding window.
+# The latent cache of a slot is a ring of R rows: position p lives in row p % R (R >= the largest window that reads it, or the
+# whole sequence length when some reader has no window).
+
+
+def latent_norm_store_ref(qc, n_q, w_ln, eps, cache, tok_slot, pos):
+    c = qc[:, n_q:].float()
+    c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * w_ln.float()
+    c = c.to(qc.dtype)
+    if cache is not None:
+        keep = tok_slot >= 0
+        cache[tok_slot[keep].long(), (pos[keep] % cache.shape[1]).long()] = c[keep].to(cache.dtype)
+    return c
+
+
+def latent_norm_store(qc, n_q: int, w_ln, eps: float, cache, tok_slot, pos):
+    """Packed prefill: c = RMSNorm(qc[:, n_q:]) * w_ln (one group, fp32 math) -> [T, rank] in qc's dtype, also written to
+    cache[tok_slot[t], pos[t] % R] for tokens whose tok_slot >= 0."""
+    if use_native(qc):
+        return lib().latent_norm_store(qc, n_q, w_ln, eps, cache, tok_slot if cache is not None else None, pos)
+    return latent_norm_store_ref(qc, n_q, w_ln, eps, cache, tok_slot, pos)
+
+
+def latent_window_attention_ref(q, kv, pos, n_heads, qk, vd, scale, window):
+    """q [T, >= n_heads*qk] (leading columns used), kv [T, n_heads*(qk+vd)] = [keys | values] head by head, pos [T]."""
+    T = q.shape[0]
+    qh = q[:, : n_heads * qk].float().reshape(T, n_heads, qk)
+    kh = kv[:, : n_heads * qk].float().reshape(T, n_heads, qk)
+    vh = kv[:, n_heads * qk:].float().reshape(T, n_heads, vd)
+    att = torch.einsum("ihd,jhd->hij", qh, kh) * scale
+    idx = torch.arange(T, device=q.device)
+    dist = idx[:, None] - idx[None, :]
+    ok = (dist >= 0) & (dist <= pos.long()[:, None])
+    if window is not None:
+        ok &= dist < window
+    att = att.masked_fill(~ok[None], float("-inf"))
+    return torch.einsum("hij,jhd->ihd", torch.softmax(att, -1), vh).reshape(T, n_heads * vd).to(q.dtype)
+
+
+def latent_window_attention(q, kv, pos, n_heads: int, qk: int, vd: int, scale: float, window: Optional[int]):
+    """Packed prefill attention: token t attends the tokens t - d of its own sequence with 0 <= d <= pos[t] and d < window.
+    Scores, softmax and the weighted sum are fp32.  Returns [T, n_heads * vd] in q's dtype."""
+    if use_native(q):
+        return lib().latent_window_attention(q, kv, pos, n_heads, qk, vd, scale, window if window is not None else 0)
+    return latent_window_attention_ref(q, kv, pos, n_heads, qk, vd, scale, window)
+
+
+def latent_decode_attention_ref(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale, window, eps):
+    B = qc.shape[0]
+    n_q = n_heads * qk
+    R = cache.shape[1]
+    idx = slots.long() if slots is not None else torch.arange(B, device=qc.device)
+    pos = cache_lens[idx].long()
+    if w_ln is not None:
+        c = qc[:, n_q:].float()
+        c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * w_ln.float()
+        cache[idx, pos % R] = c.to(cache.dtype)
+    wk = w_ukv[:n_q].float().reshape(n_heads, qk, -1)
+    wv = w_ukv[n_q:].float().reshape(n_heads, vd, -1)
+    out = torch.empty(B, n_heads * vd, dtype=torch.float32, device=qc.device)
+    for b in range(B):
+        p = int(pos[b])
+        lo = 0 if window is None else max(0, p - window + 1)
+        rows = torch.arange(lo, p + 1, device=qc.device) % R
+        cw = cache[idx[b], rows].float()                                  # [n, rank]
+        qa = torch.einsum("hd,hdr->hr", qc[b, :n_q].float().reshape(n_heads, qk), wk)   # queries absorbed into the latent space
+        pr = torch.softmax((qa @ cw.t()) * scale, -1)                     # [h, n]
+        out[b] = torch.einsum("hr,hvr->hv", pr @ cw, wv).reshape(-1)
+    return out.to(qc.dtype)
+
+
+def latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads: int, qk: int, vd: int, scale: float,
+                            window: Optional[int], eps: float):
+    """One decode step of latent attention for B rows.  qc [B, n_heads*qk (+ rank)] is the fused query | latent projection of
+    the new token, whose position is cache_lens[slot].  With `w_ln` the row's latent is normalised and written to the cache
+    first (a block that projects its own latent); without, the cache already holds it (a block that reads another block's).
+    Keys and values are never formed: the query is multiplied into the latent space (q W_uk), scores and the weighted sum run
+    over the cached latents of the window, and W_uv is applied to the result.  Does not advance cache_lens."""
+    if use_native(qc):
+        return lib().latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale,
+                                             window if window is not None else 0, eps)
+    return latent_decode_attention_ref(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale, window, eps)

@@ -571,3 +571,106 @@ def set_intervals(src: torch.Tensor, dst: torch.Tensor, intervals: List[Tuple[in
         acc += ln
     assert acc == src.numel() * es
     SegmentPlan(src_off, [a * es for a, _ in intervals], lens, dst.device).run(src, dst)
+
+
+# ------------------------------------------------------------------------------------------------ grouped norm / short conv / caps
+# Mechanisms of heterogeneous stacks (`ReaLModelConfig.blocks`): each is a PyTorch reference for CPU tensors and a kernel of
+# `csrc/seqmix.cu` for CUDA tensors.  All of them compute in fp32 whatever the tensors' dtypes.
+
+_DT_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def group_rmsnorm_ref(x, w, groups: int, eps: float):
+    """fp32 [.., W]: x cut into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), times w."""
+    shp = x.shape
+    p = x.float().reshape(*shp[:-1], groups, shp[-1] // groups)
+    p = p * torch.rsqrt(p.pow(2).mean(-1, keepdim=True) + eps)
+    return p.reshape(shp) * w.float()
+
+
+def sublayer_input_ref(x, w, groups, eps, conv_w, pos, out_dtype, state=None, tok_slot=None, remain=None):
+    n = group_rmsnorm_ref(x, w, groups, eps)
+    h = n
+    if conv_w is not None:
+        taps = conv_w.shape[1]
+        cw = conv_w.float()
+        h = n * cw[:, taps - 1]
+        for back in range(1, taps):
+            prev = torch.zeros_like(n)
+            prev[back:] = n[:-back]
+            ok = (pos.long() >= back).unsqueeze(-1)      # the source row belongs to the same sequence
+            h = h + torch.where(ok, prev, torch.zeros_like(prev)) * cw[:, taps - 1 - back]
+        h = h + n
+        if state is not None and tok_slot is not None:
+            keep = (remain < taps - 1) & (tok_slot >= 0)
+            state[tok_slot[keep].long(), (taps - 2 - remain[keep]).long()] = n[keep]
+    return h.to(out_dtype)
+
+
+def sublayer_input(x, w, groups: int, eps: float, conv_w, pos, out_dtype, state=None, tok_slot=None, remain=None):
+    """What a sublayer of a packed batch reads: n = grouped RMSNorm(x) * w, then h_t = n_t + sum_j conv_w[:, j] * n_(t - taps + 1 + j)
+    over the tokens of the same sequence (zeros before its start; `pos` [T] int32 = position inside the sequence).  conv_w None:
+    h = n.  With `state` [n_slots, taps - 1, W] fp32, the n of the last taps - 1 tokens of every sequence is left in
+    state[tok_slot[t]] (oldest first; rows of a shorter sequence are not written, the slot manager zeroes them), `remain[t]`
+    being the number of tokens that follow t in its sequence."""
+    if use_native(x):
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        lib().sublayer_input(x.contiguous(), w, conv_w, pos, out, state if conv_w is not None else None,
+                             tok_slot if state is not None else None, remain if state is not None else None, groups, eps)
+        return out
+    return sublayer_input_ref(x, w, groups, eps, conv_w, pos, out_dtype, state, tok_slot, remain)
+
+
+def sublayer_input_step_ref(x, w, groups, eps, conv_w, state, slots, out_dtype):
+    n = group_rmsnorm_ref(x, w, groups, eps)
+    if conv_w is None:
+        return n.to(out_dtype)
+    taps = conv_w.shape[1]
+    cw = conv_w.float()
+    idx = slots.long() if slots is not None else torch.arange(x.shape[0], device=x.device)
+    st = state[idx]                                                   # [B, taps - 1, W], oldest first
+    h = n + n * cw[:, taps - 1] + (st * cw[:, : taps - 1].t().unsqueeze(0)).sum(1)
+    state[idx] = torch.cat([st[:, 1:], n.unsqueeze(1)], 1)
+    return h.to(out_dtype)
+
+
+def sublayer_input_step(x, w, groups: int, eps: float, conv_w, state, slots, out_dtype):
+    """Decode form of `sublayer_input` (one token per row): the earlier inputs come from state[slots[b]] ([taps - 1, W] fp32,
+    oldest first), which is then shifted by one with this token's n appended.  slots None = row b uses slot b."""
+    if use_native(x):
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        lib().sublayer_input_step(x.contiguous(), w, conv_w, out, state if conv_w is not None else None, slots, groups, eps)
+        return out
+    return sublayer_input_step_ref(x, w, groups, eps, conv_w, state, slots, out_dtype)
+
+
+def residual_add_norm_(x, y, w, groups: int, eps: float):
+    """x += grouped RMSNorm(y) * w in place (w None: x += y).  The sum is formed in fp32 and stored in x's dtype."""
+    if use_native(x):
+        lib().residual_add_norm_(x, y.contiguous(), w, groups, eps)
+        return x
+    x.copy_((x.float() + (group_rmsnorm_ref(y, w, groups, eps) if w is not None else y.float())).to(x.dtype))
+    return x
+
+
+def clamped_glu_ref(gu, limit: float, alpha: float):
+    F_ = gu.shape[-1] // 2
+    g = gu[..., :F_].float().clamp(max=limit)
+    u = gu[..., F_:].float().clamp(min=-limit, max=limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)
+
+
+def clamped_glu(gu, limit: float, alpha: float = 1.702):
+    """g * sigmoid(alpha g) * (u + 1) on the fused [.., 2F] gate|up projection, g = min(gate, limit), u = clamp(up, +-limit)."""
+    if use_native(gu):
+        return lib().clamped_glu(gu.contiguous(), limit, alpha)
+    return clamped_glu_ref(gu, limit, alpha)
+
+
+def softcap_logits(logits, cap: Optional[float]):
+    """fp32 cap * tanh(logits / cap) (cap None: the fp32 logits)."""
+    if cap is None:
+        return logits.float()
+    if use_native(logits):
+        return lib().softcap(logits.contiguous(), cap)
+    return cap * torch.tanh(logits.float() / cap)
