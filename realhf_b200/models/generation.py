@@ -287,6 +287,7 @@ class StepSession:
         st.cache_lens[slots.long()] += 1
         return h
 
+    @torch.no_grad()
     def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
         return _final_logits(self.model, hidden_rows).float()
 

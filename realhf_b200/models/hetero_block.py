@@ -69,7 +69,8 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta) -> t
     qc = OF.linear(h, p[f"{i}.attn.q_dkv.weight"])
     n_q = a.n_heads * a.qk_dim
     if a.kv_from is None:
-        lat = attn_ops.latent_norm_store(qc, n_q, p[f"{i}.attn.dkv_ln.weight"], eps, meta.k[li] if keep else None, meta.tok_slot, meta.pos)
+        lat = attn_ops.latent_norm_store(qc, n_q, p[f"{i}.attn.dkv_ln.weight"], eps, meta.k[li] if keep else None, meta.tok_slot, meta.pos,
+                                         meta.remain)
         meta.latents[i - 1] = lat
     else:
         lat = meta.latents[a.kv_from]

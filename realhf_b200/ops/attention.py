@@ -188,22 +188,24 @@ def decode_attention(qkv, k_cache, v_cache, cache_lens, n_q: int, n_kv: int, hd:
 # whole sequence length when some reader has no window).
 
 
-def latent_norm_store_ref(qc, n_q, w_ln, eps, cache, tok_slot, pos):
+def latent_norm_store_ref(qc, n_q, w_ln, eps, cache, tok_slot, pos, remain):
     c = qc[:, n_q:].float()
     c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * w_ln.float()
     c = c.to(qc.dtype)
     if cache is not None:
-        keep = tok_slot >= 0
+        keep = (tok_slot >= 0) & (remain < cache.shape[1])
         cache[tok_slot[keep].long(), (pos[keep] % cache.shape[1]).long()] = c[keep].to(cache.dtype)
     return c
 
 
-def latent_norm_store(qc, n_q: int, w_ln, eps: float, cache, tok_slot, pos):
+def latent_norm_store(qc, n_q: int, w_ln, eps: float, cache, tok_slot, pos, remain):
     """Packed prefill: c = RMSNorm(qc[:, n_q:]) * w_ln (one group, fp32 math) -> [T, rank] in qc's dtype, also written to
-    cache[tok_slot[t], pos[t] % R] for tokens whose tok_slot >= 0."""
+    cache[tok_slot[t], pos[t] % R] for the tokens with tok_slot >= 0 that are among the last R of their sequence
+    (`remain[t]` < R: earlier positions would overwrite ring rows that later ones own)."""
     if use_native(qc):
-        return lib().latent_norm_store(qc, n_q, w_ln, eps, cache, tok_slot if cache is not None else None, pos)
-    return latent_norm_store_ref(qc, n_q, w_ln, eps, cache, tok_slot, pos)
+        return lib().latent_norm_store(qc, n_q, w_ln, eps, cache, tok_slot if cache is not None else None, pos,
+                                       remain if cache is not None else None)
+    return latent_norm_store_ref(qc, n_q, w_ln, eps, cache, tok_slot, pos, remain)
 
 
 def latent_window_attention_ref(q, kv, pos, n_heads, qk, vd, scale, window):

@@ -38,8 +38,8 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC",
     "-Xptxas", "-v", "--use_fast_math",
 ]
-# kernels that must keep IEEE division / exact expf (optimizer, norms) opt out of fast-math
-NO_FAST_MATH = {"adam.cu"}
+# kernels that must keep IEEE division / exact expf (optimizer, the fp32-exact mechanisms of heterogeneous stacks) opt out of fast-math
+NO_FAST_MATH = {"adam.cu", "seqmix.cu", "latent_attn.cu"}
 
 
 def _cutlass_include() -> list[str]:
