@@ -315,7 +315,15 @@ def main():
     ap.add_argument("--gen-fp8", action="store_true",
                     help="NOT the headline precision: decode with e4m3 weights / activations (GenerationHyperparameters.fp8_weights); "
                          "the JSON line is labelled and carries no vs_baseline")
+    ap.add_argument("--serve-bench", default="", choices=["", "rapodra"],
+                    help="NOT the headline workload: prefill / decode throughput of the named heterogeneous-stack design next to a LLaMA of "
+                         "equal size, and the roofline position of its kernels (one JSON line per result; 1 GPU)")
+    ap.add_argument("--serve-sizes", default="", help="--serve-bench only: comma-separated size names (default: all)")
     args = ap.parse_args()
+    if args.serve_bench:
+        from realhf_b200.apps import serve_bench
+        serve_bench.run(args.serve_bench, [x for x in args.serve_sizes.split(",") if x] or None)
+        return
     if args.impl == "reference":
         return run_reference(args)
     if args.impl == "torchlib":

@@ -371,12 +371,17 @@ def generate(model: ReaLModel, input_ids: torch.Tensor, cu_seqlens: torch.Tensor
     if use_graph and state.graph is None:
         state.input_ids.copy_(nxt)
         lens_backup = state.cache_lens.clone()
+        # a heterogeneous stack's step also shifts the convolution state (the cache append at `cache_lens` is idempotent)
+        conv_backup = [v.clone() for v in state.v] if state.hetero else None
         s = torch.cuda.Stream(dev)
         s.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(s):
             one_step()  # warm-up outside capture (allocations, lazy inits)
         torch.cuda.current_stream(dev).wait_stream(s)
         state.cache_lens.copy_(lens_backup)
+        if conv_backup is not None:
+            for v, b_ in zip(state.v, conv_backup):
+                v.copy_(b_)
         graph = torch.cuda.CUDAGraph()
         launches.begin_capture()
         with torch.cuda.graph(graph):

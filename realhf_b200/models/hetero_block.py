@@ -32,9 +32,12 @@ class PackedMeta:
     k: Optional[List[torch.Tensor]] = None   # DecodeState.k / .v, indexed by local block
     v: Optional[List[torch.Tensor]] = None
     latents: Dict[int, torch.Tensor] = dataclasses.field(default_factory=dict)   # block index (0-based) -> packed latent [T, rank]
+    cu_seqlens: Optional[torch.Tensor] = None
+    max_seqlen: Optional[int] = None
 
 
-def packed_meta(cu_seqlens: torch.Tensor, total: int, slots: Optional[torch.Tensor] = None, state=None) -> PackedMeta:
+def packed_meta(cu_seqlens: torch.Tensor, total: int, slots: Optional[torch.Tensor] = None, state=None,
+                max_seqlen: Optional[int] = None) -> PackedMeta:
     dev = cu_seqlens.device
     idx = torch.arange(total, device=dev, dtype=torch.int32)
     seq = torch.searchsorted(cu_seqlens[1:].contiguous(), idx, right=True).clamp_(max=cu_seqlens.numel() - 2).long()
@@ -44,7 +47,8 @@ def packed_meta(cu_seqlens: torch.Tensor, total: int, slots: Optional[torch.Tens
         tok_slot = torch.full((total,), -1, dtype=torch.int32, device=dev)
     else:
         tok_slot = slots.to(dev).int()[seq].contiguous()
-    return PackedMeta(pos, remain, tok_slot, state.k if state is not None else None, state.v if state is not None else None)
+    return PackedMeta(pos, remain, tok_slot, state.k if state is not None else None, state.v if state is not None else None,
+                      cu_seqlens=cu_seqlens.int().contiguous(), max_seqlen=max_seqlen)
 
 
 def _mlp(model, i: int, h: torch.Tensor, mcfg) -> torch.Tensor:
@@ -75,7 +79,7 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta) -> t
     else:
         lat = meta.latents[a.kv_from]
     kv = OF.linear(lat, p[f"{i}.attn.ukv.weight"])
-    o = attn_ops.latent_window_attention(qc, kv, meta.pos, a.n_heads, a.qk_dim, a.v_dim, a.scale, a.window)
+    o = attn_ops.latent_window_attention(qc, kv, meta.pos, a.n_heads, a.qk_dim, a.v_dim, a.scale, a.window, meta.cu_seqlens, meta.max_seqlen)
     y = OF.linear(o, p[f"{i}.attn.o.weight"])
     OF.residual_add_norm_(x, y, p.get(f"{i}.attn.ln_post.weight"), G, eps)
     if b.mlp is not None:

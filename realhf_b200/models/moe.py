@@ -196,13 +196,27 @@ def moe_forward(model, i: int, h: torch.Tensor, mcfg=None) -> torch.Tensor:
             0, tok[sel], (y_sorted * w_sorted[sel].to(y_sorted.dtype).unsqueeze(-1)).to(h.dtype))
         return TP.reduce_from_tp(out, ctx)
     x_sorted = h.index_select(0, tok)
-    if mcfg.use_grouped_gemm and _use_grouped_kernel(x_sorted, w_gu, w_dn):   # use_grouped_gemm=False: one GEMM pair per expert
+    grouped = mcfg.use_grouped_gemm and _use_grouped_kernel(x_sorted, w_gu, w_dn)   # use_grouped_gemm=False: one GEMM pair per expert
+    if not grouped and h.is_cuda and torch.cuda.is_current_stream_capturing():
+        # operands the grouped kernel does not take (fp32) inside a CUDA-graph capture, where the per-expert loop's host read of
+        # the counts is illegal: every expert runs on every row (decode batches are small) and the routing weight, zero for
+        # the experts a row did not choose, selects; summed in expert order
+        gate = torch.zeros(T, E, dtype=torch.float32, device=h.device).scatter_(1, idx, probs.float())
+        out = torch.zeros(T, H, dtype=torch.float32 if c.fp32_residual else h.dtype, device=h.device)
+        for e in range(E):
+            y = OF.linear(OF.gated_act(OF.linear(h, w_gu[e]), c.activation_function), w_dn[e])
+            out += (y.float() * gate[:, e: e + 1]).to(out.dtype)
+        return out
+    if grouped:
         y_sorted = grouped_mlp_device(x_sorted, _count_experts(flat_e, E), w_gu, w_dn, c.activation_function)
     else:
         counts = torch.bincount(flat_e, minlength=E).tolist()
         y_sorted = grouped_mlp(x_sorted, counts, w_gu, w_dn, c.activation_function)
     if c.fp32_residual:
-        out = torch.zeros(T, H, dtype=torch.float32, device=h.device).index_add_(0, tok, y_sorted.float() * w_sorted.unsqueeze(-1))
+        # fp32 combine in a fixed order (an atomic index_add_ would make the sum depend on the run): rows back to (token, choice)
+        # order, then the sum over the k choices
+        back = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=order.device))
+        out = (y_sorted.float() * w_sorted.unsqueeze(-1)).index_select(0, back).view(T, k, H).sum(1)
     else:
         out = torch.zeros(T, H, dtype=y_sorted.dtype, device=h.device).index_add_(0, tok, y_sorted * w_sorted.to(y_sorted.dtype).unsqueeze(-1))
     if ctx.tp_size > 1:  # experts are F-sharded over TP: partial sums

@@ -546,7 +546,7 @@ class ReaLModel(nn.Module):
             self.reload()  # offloaded by an OffloadHook after its last call: bring the weights back on first use
         cu_seqlens = cu_seqlens.int()
         if c.blocks is not None:
-            return self._forward_hetero(input_ids, cu_seqlens, hidden, kv_sink)
+            return self._forward_hetero(input_ids, cu_seqlens, hidden, kv_sink, max_seqlen)
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         T = int(input_ids.shape[0]) if input_ids is not None else None
@@ -584,7 +584,7 @@ class ReaLModel(nn.Module):
             x = TP.gather_from_sp(x, self.ctx, reduce_scatter_bwd=False)
         return ModelOutput(hidden=x, head_weight=self.head_weight(), ctx=self.ctx, is_critic=c.is_critic)
 
-    def _forward_hetero(self, input_ids, cu_seqlens, hidden, kv_sink):
+    def _forward_hetero(self, input_ids, cu_seqlens, hidden, kv_sink, max_seqlen=None):
         """Packed forward of a heterogeneous stack (inference only: its kernels have no backward)."""
         from realhf_b200.models import hetero_block as HB
         c = self.config
@@ -592,7 +592,9 @@ class ReaLModel(nn.Module):
             "heterogeneous stacks are inference-only"
         T = int(input_ids.shape[0]) if input_ids is not None else int(hidden.shape[0])
         state, slots = kv_sink if kv_sink is not None else (None, None)
-        meta = HB.packed_meta(cu_seqlens, T, slots, state)
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        meta = HB.packed_meta(cu_seqlens, T, slots, state, max_seqlen)
         x, li = hidden, 0
         with torch.no_grad():
             for i in self.layers:

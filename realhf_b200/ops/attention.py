@@ -224,10 +224,28 @@ def latent_window_attention_ref(q, kv, pos, n_heads, qk, vd, scale, window):
     return torch.einsum("hij,jhd->ihd", torch.softmax(att, -1), vh).reshape(T, n_heads * vd).to(q.dtype)
 
 
-def latent_window_attention(q, kv, pos, n_heads: int, qk: int, vd: int, scale: float, window: Optional[int]):
+def _tcgen05_window_ok(q, kv, n_heads, qk, vd) -> bool:
+    """The tcgen05 varlen kernel takes 16-bit operands with equal query / value head dims of 64 or 128 and 16-byte aligned rows."""
+    return (os.environ.get("REAL_LATENT_ATTN", "tcgen05") == "tcgen05" and q.dtype in (torch.bfloat16, torch.float16) and qk == vd
+            and qk in (64, 128) and q.stride(1) == 1 and kv.stride(1) == 1 and q.stride(0) % 8 == 0 and kv.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and kv.data_ptr() % 16 == 0)
+
+
+def latent_window_attention(q, kv, pos, n_heads: int, qk: int, vd: int, scale: float, window: Optional[int], cu_seqlens=None,
+                            max_seqlen: Optional[int] = None):
     """Packed prefill attention: token t attends the tokens t - d of its own sequence with 0 <= d <= pos[t] and d < window.
-    Scores, softmax and the weighted sum are fp32.  Returns [T, n_heads * vd] in q's dtype."""
+    Scores and softmax are fp32.  Returns [T, n_heads * vd] in q's dtype.  CUDA: 16-bit operands with equal head dims of 64 / 128
+    run the tcgen05 varlen kernel with its sliding-window mask (needs `cu_seqlens`, `max_seqlen`; the softmax weights are rounded
+    to the operand type for the P V product on the tensor cores, like the V operand itself); every other shape, and fp32, runs
+    the CUDA-core kernel of `csrc/latent_attn.cu`, which keeps the weights and the sum in fp32."""
     if use_native(q):
+        if cu_seqlens is not None and max_seqlen is not None and _tcgen05_window_ok(q, kv, n_heads, qk, vd):
+            T = q.shape[0]
+            qv = q[:, : n_heads * qk].view(T, n_heads, qk)
+            kk = kv[:, : n_heads * qk].view(T, n_heads, qk)
+            vv = kv[:, n_heads * qk:].view(T, n_heads, vd)
+            out = lib().attn_fwd_window(qv, kk, vv, cu_seqlens, max_seqlen, scale, True, window if window is not None else 0)[0]
+            return out.view(T, n_heads * vd)
         return lib().latent_window_attention(q, kv, pos, n_heads, qk, vd, scale, window if window is not None else 0)
     return latent_window_attention_ref(q, kv, pos, n_heads, qk, vd, scale, window)
 

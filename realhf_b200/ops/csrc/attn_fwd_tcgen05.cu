@@ -2,6 +2,10 @@
 //
 //   O[t, h, :] = softmax(scale * Q[t, h, :] K[seq(t), kv(h), :]^T  (+ causal mask)) V        bf16 / fp16, fp32 softmax
 //
+// Optional sliding window (causal only): query i sees keys (i - window, i].  Key tiles that lie wholly below the window of the
+// CTA's first query row are never loaded (all three roles walk the same tile range [tile0, tile0 + n_kv)); inside the
+// remaining tiles the lower edge is a per-row column mask like the diagonal.
+//
 // Reference: flash-attn's `flash_attn_varlen_func` called from `impl/model/modules/attn.py:240-262`.  One CTA owns a
 // 128-row query tile of one (sequence, head) and walks the key / value tiles of that sequence (up to the diagonal).
 //
@@ -37,6 +41,7 @@ struct AttnParams {
   int T, nq, nkv;
   float scale;
   int causal;
+  int window;             // > 0 (with causal): a query at position i sees keys (i - window, i]
 };
 
 template <int kD> struct ACfg {
@@ -76,7 +81,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   if (q0 >= L) return;  // uniform for the CTA, before any barrier / TMEM allocation
   const int hk = head / (p.nq / p.nkv);
   const int kv_len = p.causal ? min(L, q0 + kBQ) : L;
-  const int n_kv = RB_CEIL_DIV(kv_len, kBKV);
+  const int win = (p.causal && p.window > 0) ? p.window : 0;
+  const int tile0 = win > 0 ? max(0, q0 - win + 1) / kBKV : 0;   // first key tile any row of this CTA can see
+  const int n_kv = RB_CEIL_DIV(kv_len, kBKV) - tile0;             // >= 1: the diagonal tile is always visible
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -118,7 +125,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t par = (uint32_t)(j >> 1) & 1u;
-        const int row = tok0 + j * kBKV;
+        const int row = tok0 + (tile0 + j) * kBKV;
         ptx::mbar_wait(bar(K_EMPTY + st), par ^ 1);
         ptx::mbar_arrive_expect_tx(bar(K_FULL + st), C::kKVBytes);
 #pragma unroll
@@ -213,12 +220,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 
     for (int j = 0; j < n_kv; ++j) {
       const int b = j & 1;
-      const int kv0 = j * kBKV;
+      const int kv0 = (tile0 + j) * kBKV;
       ptx::mbar_wait(bar(S_FULL + b), (uint32_t)(j >> 1) & 1u);
       ptx::tc_fence_after();
-      // only the last tile of the sequence and the diagonal tile need per-element masks (uniform over the CTA)
-      const bool need_mask = (kv0 + kBKV > L) || (p.causal && kv0 + kBKV - 1 > q0);
-      const int lim = (p.causal ? min(L, q_pos + 1) : L) - kv0;  // local key columns [0, lim) are visible to this row
+      // only the last tile of the sequence, the diagonal tile and the tiles the window's lower edge crosses need per-element
+      // masks (uniform over the CTA)
+      const bool need_mask = (kv0 + kBKV > L) || (p.causal && kv0 + kBKV - 1 > q0) || (win > 0 && q0 + kBQ - win > kv0);
+      const int lim = (p.causal ? min(L, q_pos + 1) : L) - kv0;  // local key columns [lo, lim) are visible to this row
+      const int lo = win > 0 ? q_pos - win + 1 - kv0 : 0;
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < kBKV / 32; ++c) {
@@ -228,7 +237,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float s = __uint_as_float(r[i]);
-          if (need_mask && c * 32 + i >= lim) s = -INFINITY;
+          if (need_mask && (c * 32 + i >= lim || c * 32 + i < lo)) s = -INFINITY;
           mx = fmaxf(mx, s);
         }
       }
@@ -249,8 +258,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           float e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, neg_m));
           float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, neg_m));
           if (need_mask) {
-            if (c * 32 + i >= lim) e0 = 0.f;
-            if (c * 32 + i + 1 >= lim) e1 = 0.f;
+            if (c * 32 + i >= lim || c * 32 + i < lo) e0 = 0.f;
+            if (c * 32 + i + 1 >= lim || c * 32 + i + 1 < lo) e1 = 0.f;
           }
           sum += e0 + e1;
           w[i >> 1] = pack2<T>(e0, e1);
@@ -320,9 +329,10 @@ int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
 // q / k / v: [T, heads, hd] views (unit stride over hd, `heads * hd` contiguous columns, row pitch *_ld elements) -- e.g. the
 // three column ranges of the fused QKV projection.  out [T, nq, hd] with row pitch out_ld, lse [nq, T] fp32.
 // dt: 1 = bf16, 2 = fp16.  Returns 0 or a negative code (unsupported shape / descriptor failure).
-extern "C" int rb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
-                           int64_t q_ld, int64_t k_ld, int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd,
-                           int max_seqlen, float scale, int causal, int dt, cudaStream_t s) {
+// window > 0 (causal only): sliding-window attention.
+extern "C" int rb_attn_fwd_window(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
+                                  int64_t q_ld, int64_t k_ld, int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd,
+                                  int max_seqlen, float scale, int causal, int window, int dt, cudaStream_t s) {
   if (hd != 128 && hd != 64) return -1;
   if (dt != 1 && dt != 2) return -2;
   if (nq % nkv != 0 || T <= 0 || B <= 0 || max_seqlen <= 0) return -3;
@@ -333,11 +343,18 @@ extern "C" int rb_attn_fwd(const void* q, const void* k, const void* v, void* ou
   if (!make_tmap(&mq, q, bf, T, (uint64_t)nq * hd, q_ld, 64, kBQ)) return -10;
   if (!make_tmap(&mk, k, bf, T, (uint64_t)nkv * hd, k_ld, 64, kBKV)) return -11;
   if (!make_tmap(&mv, v, bf, T, (uint64_t)nkv * hd, v_ld, 64, 64)) return -12;  // 64-key halves, see the producer
-  AttnParams p{cu_seqlens, out, lse, out_ld, T, nq, nkv, scale, causal};
+  if (window > 0 && !causal) return -6;
+  AttnParams p{cu_seqlens, out, lse, out_ld, T, nq, nkv, scale, causal, window};
   if (hd == 128) {
     return bf ? launch_attn_fwd<128, __nv_bfloat16, 1>(mq, mk, mv, p, B, max_seqlen, s)
               : launch_attn_fwd<128, __half, 0>(mq, mk, mv, p, B, max_seqlen, s);
   }
   return bf ? launch_attn_fwd<64, __nv_bfloat16, 1>(mq, mk, mv, p, B, max_seqlen, s)
             : launch_attn_fwd<64, __half, 0>(mq, mk, mv, p, B, max_seqlen, s);
+}
+
+extern "C" int rb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
+                           int64_t q_ld, int64_t k_ld, int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd,
+                           int max_seqlen, float scale, int causal, int dt, cudaStream_t s) {
+  return rb_attn_fwd_window(q, k, v, out, lse, cu_seqlens, q_ld, k_ld, v_ld, out_ld, T, B, nq, nkv, hd, max_seqlen, scale, causal, 0, dt, s);
 }

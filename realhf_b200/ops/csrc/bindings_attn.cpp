@@ -91,10 +91,23 @@ extern "C" int rb_attn_fwd(const void* q, const void* k, const void* v, void* ou
                            int64_t k_ld, int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd, int max_seqlen,
                            float scale, int causal, int dt, cudaStream_t s);
 
+extern "C" int rb_attn_fwd_window(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens, int64_t q_ld,
+                                  int64_t k_ld, int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd, int max_seqlen,
+                                  float scale, int causal, int window, int dt, cudaStream_t s);
+
+std::vector<Tensor> attn_fwd_window(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_seqlens, int64_t max_seqlen,
+                                    double scale, bool causal, int64_t window);
+
 // q [T, nq, hd], k / v [T, nkv, hd]: views with unit stride over hd and heads packed (stride(1) == hd), any row pitch.
 // Returns (out [T, nq, hd], lse [nq, T] fp32).
 std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_seqlens, int64_t max_seqlen,
                              double scale, bool causal) {
+  return attn_fwd_window(q, k, v, cu_seqlens, max_seqlen, scale, causal, 0);
+}
+
+// The same with a sliding window (window > 0, causal): a query at position i sees keys (i - window, i].
+std::vector<Tensor> attn_fwd_window(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_seqlens, int64_t max_seqlen,
+                                    double scale, bool causal, int64_t window) {
   TORCH_CHECK(q.is_cuda() && q.dim() == 3 && k.dim() == 3 && v.dim() == 3);
   const int64_t T = q.size(0), nq = q.size(1), hd = q.size(2), nkv = k.size(1);
   for (const Tensor* t : {&q, &k, &v}) TORCH_CHECK(t->stride(2) == 1 && t->stride(1) == hd && t->size(0) == T && t->size(2) == hd);
@@ -104,9 +117,10 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
   auto out = at::empty({T, nq, hd}, q.options());
   auto lse = at::empty({nq, T}, q.options().dtype(at::kFloat));
   const int dt = q.scalar_type() == at::kBFloat16 ? 1 : (q.scalar_type() == at::kHalf ? 2 : -1);
-  int rc = rb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), cu_seqlens.data_ptr<int>(),
-                       q.stride(0), k.stride(0), v.stride(0), out.stride(0), (int)T, (int)cu_seqlens.numel() - 1, (int)nq, (int)nkv,
-                       (int)hd, (int)max_seqlen, (float)scale, causal ? 1 : 0, dt, at::cuda::getCurrentCUDAStream().stream());
+  int rc = rb_attn_fwd_window(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), cu_seqlens.data_ptr<int>(),
+                              q.stride(0), k.stride(0), v.stride(0), out.stride(0), (int)T, (int)cu_seqlens.numel() - 1, (int)nq, (int)nkv,
+                              (int)hd, (int)max_seqlen, (float)scale, causal ? 1 : 0, (int)window, dt,
+                              at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "attn_fwd: unsupported configuration (", rc, ")");
   return {out, lse};
 }
@@ -177,6 +191,7 @@ void register_attn_ops(torch::Library& m) {
   m.def("sample_graph(Tensor logits, Tensor(a!) tok_hist, Tensor(b!) lp_hist, Tensor(c!)? mask_hist, Tensor(d!) unfinished, Tensor(e!) step_rows, Tensor(f!) input_ids, Tensor(g!) cache_lens, Tensor seed, int min_new_tokens, int top_k, float top_p, float inv_temp, int eos_id, bool greedy, int pad_id) -> ()", &sample_graph);
   m.def("attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor cu_seqlens, int max_seqlen, float scale, bool causal) -> ()", &attn_bwd);
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float scale, bool causal) -> Tensor[]", &attn_fwd);
+  m.def("attn_fwd_window(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float scale, bool causal, int window) -> Tensor[]", &attn_fwd_window);
   m.def("sample(Tensor logits, Tensor? unfinished, int top_k, float top_p, float inv_temp, int eos_id, bool suppress_eos, bool greedy, int pad_id, int seed, int step, bool want_mask) -> Tensor[]", &sample);
   m.def("decode_attention(Tensor qkv, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor cache_lens, int nq, int nkv, int hd, float scale, Tensor? cos, Tensor? sin, int rot_dim, bool interleaved) -> Tensor", &decode_attention);
 }
