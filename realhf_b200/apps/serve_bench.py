@@ -127,7 +127,11 @@ def kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx: int, de
     q = torch.randn(T, H * qk + rank, device=dev).to(bf)
     kv = torch.randn(T, H * (qk + vd), device=dev).to(bf)
     pairs = batch * sum(min(p + 1, win) for p in range(prompt_len))
-    add("latent_window_attention (prefill)", False, _time(lambda: A.latent_window_attention(q, kv, meta.pos, H, qk, vd, qk ** -0.5, win), 5, flush=flush),
+    add("latent_window_attention (prefill, tcgen05 kernel with window)", False,
+        _time(lambda: A.latent_window_attention(q, kv, meta.pos, H, qk, vd, qk ** -0.5, win, cu, prompt_len), 5, flush=flush),
+        T * H * (2 * qk + 2 * vd) * 2, 2.0 * pairs * H * (qk + vd))
+    add("latent_window_attention (prefill, CUDA-core kernel: fp32 and other head shapes)", False,
+        _time(lambda: A.latent_window_attention(q, kv, meta.pos, H, qk, vd, qk ** -0.5, win), 2, warmup=1, flush=flush),
         T * H * (2 * qk + 2 * vd) * 2, 2.0 * pairs * H * (qk + vd))
     qkv = torch.randn(T, 3 * H * qk, device=dev).to(bf)
     full_pairs = batch * prompt_len * (prompt_len + 1) // 2

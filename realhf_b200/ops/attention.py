@@ -250,6 +250,19 @@ def latent_window_attention(q, kv, pos, n_heads: int, qk: int, vd: int, scale: f
     return latent_window_attention_ref(q, kv, pos, n_heads, qk, vd, scale, window)
 
 
+def _absorbed_projections(w_ukv, n_heads: int, qk: int, vd: int, scale: float):
+    """fp32 per-head forms of the fused [key | value] up-projection for decode: W_uk * scale as [H, qk, rank] (queries go INTO the
+    latent space) and W_uv^T as [H, rank, vd] (latent sums come out of it).  Cached on the weight tensor."""
+    from realhf_b200.ops.functional import cached_on
+
+    def build(w):
+        rank, n_q = w.shape[1], n_heads * qk
+        wk = (w[:n_q].reshape(n_heads, qk, rank).float() * scale).contiguous()
+        wv = w[n_q:].reshape(n_heads, vd, rank).float().transpose(1, 2).contiguous()
+        return wk, wv
+    return cached_on(w_ukv, f"_absorbed_{n_heads}_{qk}_{vd}_{float(scale)!r}", build)
+
+
 def latent_decode_attention_ref(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale, window, eps):
     B = qc.shape[0]
     n_q = n_heads * qk
@@ -282,6 +295,19 @@ def latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads: 
     Keys and values are never formed: the query is multiplied into the latent space (q W_uk), scores and the weighted sum run
     over the cached latents of the window, and W_uv is applied to the result.  Does not advance cache_lens."""
     if use_native(qc):
-        return lib().latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale,
-                                             window if window is not None else 0, eps)
+        rank, R, B = cache.shape[2], cache.shape[1], qc.shape[0]
+        if os.environ.get("REAL_LATENT_DECODE", "split") == "fused" or rank > 512:
+            # one launch per (row, head): small problems / A-B runs
+            return lib().latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale,
+                                                 window if window is not None else 0, eps)
+        n_q = n_heads * qk
+        if w_ln is not None:
+            lib().latent_append(qc, n_q, w_ln, cache, cache_lens, slots, eps)
+        wk, wv = _absorbed_projections(w_ukv, n_heads, qk, vd, scale)
+        qa = torch.bmm(qc[:, :n_q].reshape(B, n_heads, qk).transpose(0, 1).float(), wk)           # [H, B, rank] fp32
+        # enough CTAs to fill the GPU: split the keys when rows x head tiles are few (a split is at least two 32-key tiles)
+        ctas = B * ((n_heads + 15) // 16)
+        splits = max(1, min((2 * 148 + ctas - 1) // ctas, R // 64, 32))
+        o = lib().latent_decode_core(qa, cache, cache_lens, slots, window if window is not None else 0, splits)
+        return torch.bmm(o, wv).transpose(0, 1).reshape(B, n_heads * vd).to(qc.dtype)
     return latent_decode_attention_ref(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale, window, eps)

@@ -41,6 +41,9 @@ int rb_latent_window_attention(const void*, int64_t, const void*, int64_t, const
                                cudaStream_t);
 int rb_latent_decode_attention(const void*, int64_t, const void*, const void*, void*, const int*, const int*, void*, int, int, int, int, int,
                                int, float, int, float, int, cudaStream_t);
+int rb_latent_append(const void*, int64_t, int, const void*, void*, const int*, const int*, int, int, int, float, int, cudaStream_t);
+int rb_latent_decode_core(const float*, const void*, const int*, const int*, float*, float*, float*, int, int, int, int, int, int, int,
+                          cudaStream_t);
 }
 
 namespace {
@@ -56,8 +59,8 @@ void sublayer_input(const Tensor& x, const Tensor& w, const OptT& conv_w, const 
   const void* cw = nullptr;
   if (conv_w.has_value()) {
     CHECK_IN((*conv_w));
-    TORCH_CHECK(conv_w->dim() == 2 && conv_w->size(0) == W && conv_w->scalar_type() == w.scalar_type());
-    taps = conv_w->size(1);
+    TORCH_CHECK(conv_w->dim() == 2 && conv_w->size(1) == W && conv_w->scalar_type() == w.scalar_type(), "conv_w: tap-major [taps, W]");
+    taps = conv_w->size(0);
     cw = conv_w->data_ptr();
     TORCH_CHECK(taps <= 1 || pos.has_value(), "a convolution over time needs the tokens' positions");
   }
@@ -85,8 +88,8 @@ void sublayer_input_step(const Tensor& x, const Tensor& w, const OptT& conv_w, T
   float* st = nullptr;
   if (conv_w.has_value()) {
     CHECK_IN((*conv_w));
-    TORCH_CHECK(conv_w->dim() == 2 && conv_w->size(0) == W && conv_w->scalar_type() == w.scalar_type());
-    taps = conv_w->size(1);
+    TORCH_CHECK(conv_w->dim() == 2 && conv_w->size(1) == W && conv_w->scalar_type() == w.scalar_type(), "conv_w: tap-major [taps, W]");
+    taps = conv_w->size(0);
     cw = conv_w->data_ptr();
     if (taps > 1) {
       TORCH_CHECK(state.has_value(), "a convolution over time needs its state");
@@ -191,6 +194,42 @@ Tensor latent_decode_attention(const Tensor& qc, const OptT& w_ln, const Tensor&
   return out;
 }
 
+// Normalise the latent columns of qc [B, >= n_q + rank] and append them to the ring cache at position cache_lens[slot].
+void latent_append(const Tensor& qc, int64_t n_q, const Tensor& w_ln, Tensor cache, const Tensor& cache_lens, const OptT& slots, double eps) {
+  CHECK_CUDA(qc); CHECK_IN(w_ln); CHECK_IN(cache); CHECK_IN(cache_lens);
+  const int rank = cache.size(2);
+  const int64_t B = qc.size(0);
+  TORCH_CHECK(qc.dim() == 2 && qc.stride(1) == 1 && qc.size(1) >= n_q + rank && w_ln.numel() == rank && cache.dim() == 3);
+  TORCH_CHECK(cache.scalar_type() == qc.scalar_type() && w_ln.scalar_type() == qc.scalar_type() && cache_lens.scalar_type() == at::kInt);
+  TORCH_CHECK(slots.has_value() || cache.size(0) >= B);
+  c10::cuda::CUDAGuard g(qc.device());
+  const int rc = rb_latent_append(qc.data_ptr(), qc.stride(0), (int)n_q, w_ln.data_ptr(), cache.data_ptr(), cache_lens.data_ptr<int>(),
+                                  int_ptr(slots, B, "slots"), (int)B, rank, (int)cache.size(1), (float)eps, dt_code(qc), cur_stream());
+  TORCH_CHECK(rc == 0, "latent_append failed (rc ", rc, ")");
+}
+
+// qa [H, B, rank] fp32 (queries in latent space, scale applied) -> softmax-weighted sums of the cached latents [H, B, rank] fp32.
+Tensor latent_decode_core(const Tensor& qa, const Tensor& cache, const Tensor& cache_lens, const OptT& slots, int64_t window, int64_t splits) {
+  CHECK_IN(qa); CHECK_IN(cache); CHECK_IN(cache_lens);
+  TORCH_CHECK(qa.dim() == 3 && qa.scalar_type() == at::kFloat && cache.dim() == 3 && cache.size(2) == qa.size(2));
+  TORCH_CHECK(cache_lens.scalar_type() == at::kInt);
+  const int64_t H = qa.size(0), B = qa.size(1), rank = qa.size(2);
+  TORCH_CHECK(slots.has_value() || cache.size(0) >= B);
+  c10::cuda::CUDAGuard g(qa.device());
+  auto out = at::empty_like(qa);
+  Tensor pa, pm;
+  if (splits > 1) {
+    pa = at::empty({H, B, splits, rank}, qa.options());
+    pm = at::empty({H, B, splits, 2}, qa.options());
+  }
+  const int rc = rb_latent_decode_core(qa.data_ptr<float>(), cache.data_ptr(), cache_lens.data_ptr<int>(), int_ptr(slots, B, "slots"),
+                                       out.data_ptr<float>(), splits > 1 ? pa.data_ptr<float>() : nullptr,
+                                       splits > 1 ? pm.data_ptr<float>() : nullptr, (int)B, (int)H, (int)rank, (int)cache.size(1), (int)window,
+                                       (int)splits, dt_code(cache), cur_stream());
+  TORCH_CHECK(rc == 0, "latent_decode_core: unsupported shape (rc ", rc, ")");
+  return out;
+}
+
 }  // namespace
 
 void register_seq_ops(torch::Library& m) {
@@ -201,5 +240,7 @@ void register_seq_ops(torch::Library& m) {
   m.def("softcap(Tensor x, float cap) -> Tensor", &softcap);
   m.def("latent_norm_store(Tensor qc, int n_q, Tensor w_ln, float eps, Tensor(a!)? cache, Tensor? tok_slot, Tensor pos, Tensor? remain) -> Tensor", &latent_norm_store);
   m.def("latent_window_attention(Tensor q, Tensor kv, Tensor pos, int n_heads, int qk, int vd, float scale, int window) -> Tensor", &latent_window_attention);
+  m.def("latent_append(Tensor qc, int n_q, Tensor w_ln, Tensor(a!) cache, Tensor cache_lens, Tensor? slots, float eps) -> ()", &latent_append);
+  m.def("latent_decode_core(Tensor qa, Tensor cache, Tensor cache_lens, Tensor? slots, int window, int splits) -> Tensor", &latent_decode_core);
   m.def("latent_decode_attention(Tensor qc, Tensor? w_ln, Tensor w_ukv, Tensor(a!) cache, Tensor cache_lens, Tensor? slots, int n_heads, int qk, int vd, float scale, int window, float eps) -> Tensor", &latent_decode_attention);
 }

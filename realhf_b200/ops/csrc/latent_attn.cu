@@ -246,6 +246,207 @@ __global__ void __launch_bounds__(kDT) latent_decode_attention_kernel(
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------ decode, split form
+// Three steps: `latent_append` normalises and appends the new latent rows; the caller forms qa = scale * q W_uk per head with a
+// batched matrix product ([H, B, rank] fp32); `latent_decode_core` below turns (qa, cached latents) into the softmax-weighted
+// latent sums [H, B, rank] fp32, to which the caller applies W_uv.
+//
+// Core: one CTA per (row, tile of 16 heads, key split), 128 threads.  A tile of 32 latent rows is staged in shared memory as
+// fp32 and used twice: scores S[16 heads][32 keys] (thread = 1 key x 4 heads, the dot over the rank with 16-byte shared loads;
+// the qa reads are warp broadcasts) and, after an online-softmax update per head, the weighted sum into the thread's
+// 16 heads x 4 rank columns of accumulators.  With more than one split the partial (max, sum, accumulator) triples go to a
+// workspace and `latent_decode_combine` merges them.
+constexpr int kCT = 128;     // threads
+constexpr int kHT = 16;      // heads per CTA
+constexpr int kKT = 32;      // keys per tile
+constexpr int kMaxRank = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(128) latent_append_kernel(const T* __restrict__ qc, int64_t ldq, int n_q, const T* __restrict__ w,
+                                                            T* __restrict__ cache, const int* __restrict__ cache_lens,
+                                                            const int* __restrict__ slots, int B, int rank, int R, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= B) return;
+  const int64_t slot = slots != nullptr ? slots[b] : b;
+  const int pos = cache_lens[slot];
+  const T* src = qc + b * ldq + n_q;
+  float s = 0.f;
+  for (int r = lane; r < rank; r += 32) { const float v = rb::to_f(src[r]); s += v * v; }
+  s = rb::warp_sum(s);
+  const float rstd = 1.f / sqrtf(s / (float)rank + eps);
+  T* dst = cache + (slot * R + (pos % R)) * (int64_t)rank;
+  for (int r = lane; r < rank; r += 32) dst[r] = rb::from_f<T>(rb::to_f(src[r]) * rstd * rb::to_f(w[r]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __restrict__ qa, const T* __restrict__ cache,
+                                                                 const int* __restrict__ cache_lens, const int* __restrict__ slots,
+                                                                 float* __restrict__ out, float* __restrict__ part_acc,
+                                                                 float* __restrict__ part_ml, int B, int H, int rank, int R, int window,
+                                                                 int splits) {
+  extern __shared__ float sm[];
+  const int RP = ((rank + 3) & ~3) + 4;        // padded row: 16-byte aligned, rows 4 banks apart
+  float* qs = sm;                              // [kHT][RP]
+  float* cs = qs + kHT * RP;                   // [kKT][RP]
+  float* ps = cs + kKT * RP;                   // [kKT][kHT]  scores, then softmax weights
+  float* al = ps + kKT * kHT;                  // [kHT] rescale factor of the running sums for this tile
+  const int tid = threadIdx.x;
+  const int b = blockIdx.x, h0 = blockIdx.y * kHT, split = blockIdx.z;
+  const int nh = min(kHT, H - h0);
+  const int64_t slot = slots != nullptr ? slots[b] : b;
+  const int pos = cache_lens[slot];
+  const int reach = (window > 0 && window - 1 < pos) ? window - 1 : pos;
+  const int n_keys = reach + 1, lo = pos - reach;
+  const int per = RB_CEIL_DIV(RB_CEIL_DIV(n_keys, splits), kKT) * kKT;   // keys per split, whole tiles
+  const int k_begin = lo + split * per, k_end = min(pos + 1, k_begin + per);
+  for (int e = tid; e < kHT * RP; e += kCT) {
+    const int h = e / RP, r = e % RP;
+    qs[e] = (h < nh && r < rank) ? qa[((int64_t)(h0 + h) * B + b) * rank + r] : 0.f;
+  }
+  const bool vec = rank % (16 / (int)sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0;
+  if (vec)                                     // the vector fill writes columns [0, rank) only
+    for (int e = tid; e < kKT * (RP - rank); e += kCT) cs[(e / (RP - rank)) * RP + rank + e % (RP - rank)] = 0.f;
+  const int my_k = tid & 31, hg = tid >> 5;    // scores: key my_k of the tile, heads 4 hg .. 4 hg + 3
+  const int r0 = tid * 4;                      // sums: rank columns r0 .. r0 + 3 of all 16 heads
+  float acc[kHT][4];
+#pragma unroll
+  for (int h = 0; h < kHT; ++h)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[h][i] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;        // of head `tid` (threads 0 .. 15)
+  for (int kb = k_begin; kb < k_end; kb += kKT) {
+    const int nk = min(kKT, k_end - kb);
+    __syncthreads();                           // previous tile fully consumed (and qs written, first time round)
+    if (vec) {
+      // 16-byte global loads: VPT elements per thread and step; the pad columns beyond the rank stay zero from the first fill
+      constexpr int VPT = 16 / sizeof(T);
+      const int per_row = rank / VPT;
+      for (int e = tid; e < kKT * per_row; e += kCT) {
+        const int k = e / per_row, v = e - k * per_row;
+        float f[VPT];
+        if (k < nk) {
+          const rb::Pack<T, VPT> pk = *reinterpret_cast<const rb::Pack<T, VPT>*>(cache + (slot * R + ((kb + k) % R)) * (int64_t)rank + v * VPT);
+#pragma unroll
+          for (int i = 0; i < VPT; ++i) f[i] = rb::to_f(pk.v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VPT; ++i) f[i] = 0.f;
+        }
+        float4* dst = reinterpret_cast<float4*>(cs + k * RP + v * VPT);
+#pragma unroll
+        for (int i = 0; i < VPT / 4; ++i) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+      }
+    } else {
+      for (int e = tid; e < kKT * RP; e += kCT) {
+        const int k = e / RP, r = e % RP;
+        cs[e] = (k < nk && r < rank) ? rb::to_f(cache[(slot * R + ((kb + k) % R)) * (int64_t)rank + r]) : 0.f;
+      }
+    }
+    __syncthreads();
+    {
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float4* cr = reinterpret_cast<const float4*>(cs + my_k * RP);
+#pragma unroll 4
+      for (int r4 = 0; r4 < (RP - 4) / 4; ++r4) {
+        const float4 cv = cr[r4];
+#pragma unroll
+        for (int hh = 0; hh < 4; ++hh) {
+          const float4 qv = reinterpret_cast<const float4*>(qs + (hg * 4 + hh) * RP)[r4];
+          s4[hh] = fmaf(cv.x, qv.x, fmaf(cv.y, qv.y, fmaf(cv.z, qv.z, fmaf(cv.w, qv.w, s4[hh]))));
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh) ps[my_k * kHT + hg * 4 + hh] = my_k < nk ? s4[hh] : -INFINITY;
+    }
+    __syncthreads();
+    if (tid < kHT) {                           // online softmax of head `tid` over this tile
+      float mx = m_run;
+      for (int k = 0; k < nk; ++k) mx = fmaxf(mx, ps[k * kHT + tid]);
+      const float a = expf(m_run - mx);        // first tile: exp(-inf) = 0
+      float sum = 0.f;
+      for (int k = 0; k < kKT; ++k) {
+        const float p = k < nk ? expf(ps[k * kHT + tid] - mx) : 0.f;
+        ps[k * kHT + tid] = p;
+        sum += p;
+      }
+      l_run = l_run * a + sum;
+      m_run = mx;
+      al[tid] = a;
+    }
+    __syncthreads();
+    if (r0 < RP - 4) {
+#pragma unroll
+      for (int h = 0; h < kHT; ++h) {
+        const float a = al[h];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[h][i] *= a;
+      }
+      for (int k = 0; k < nk; ++k) {
+        const float4 cv = *reinterpret_cast<const float4*>(cs + k * RP + r0);
+        const float4* pk = reinterpret_cast<const float4*>(ps + k * kHT);
+#pragma unroll
+        for (int h4 = 0; h4 < kHT / 4; ++h4) {
+          const float4 pv = pk[h4];
+          const float pw[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+          for (int hh = 0; hh < 4; ++hh) {
+            acc[h4 * 4 + hh][0] = fmaf(pw[hh], cv.x, acc[h4 * 4 + hh][0]);
+            acc[h4 * 4 + hh][1] = fmaf(pw[hh], cv.y, acc[h4 * 4 + hh][1]);
+            acc[h4 * 4 + hh][2] = fmaf(pw[hh], cv.z, acc[h4 * 4 + hh][2]);
+            acc[h4 * 4 + hh][3] = fmaf(pw[hh], cv.w, acc[h4 * 4 + hh][3]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < kHT) { al[tid] = l_run; ps[tid] = m_run; }
+  __syncthreads();
+  if (splits == 1) {
+#pragma unroll
+    for (int h = 0; h < kHT; ++h) {
+      if (h >= nh) break;
+      const float inv = 1.f / al[h];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (r0 + i < rank) out[((int64_t)(h0 + h) * B + b) * rank + r0 + i] = acc[h][i] * inv;
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < kHT; ++h) {
+      if (h >= nh) break;
+      const int64_t row = ((int64_t)(h0 + h) * B + b) * splits + split;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (r0 + i < rank) part_acc[row * rank + r0 + i] = acc[h][i];
+      if (tid == 0) { part_ml[row * 2] = ps[h]; part_ml[row * 2 + 1] = al[h]; }
+    }
+  }
+}
+
+// out[h, b, :] = sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M); a split without keys has m = -inf, l = 0.
+__global__ void __launch_bounds__(128) latent_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                                    float* __restrict__ out, int rank, int splits) {
+  const int64_t row = blockIdx.x;      // (h, b)
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(row * splits + s) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = part_ml[(row * splits + s) * 2];
+    if (m != -INFINITY) L += part_ml[(row * splits + s) * 2 + 1] * expf(m - M);
+  }
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = part_ml[(row * splits + s) * 2];
+      if (m != -INFINITY) o += part_acc[(row * splits + s) * rank + r] * expf(m - M);
+    }
+    out[row * rank + r] = o / L;
+  }
+}
+
 template <typename T, int NACC>
 int launch_prefill(const void* q, int64_t ldq, const void* kv, int64_t ldkv, const int* pos, void* out, int64_t n_tok, int H, int qk, int vd,
                    float scale, int window, cudaStream_t s) {
@@ -305,6 +506,35 @@ int rb_latent_decode_attention(const void* qc, int64_t ldq, const void* w_ln, co
   RB_DISPATCH_T(dt, (latent_decode_attention_kernel<T><<<grid, kDT, smem, s>>>((const T*)qc, ldq, (const T*)w_ln, (const T*)w_ukv, (T*)cache,
                                                                                 cache_lens, slots, (T*)out, H, qk, vd, rank, R, scale, window, eps)));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int rb_latent_append(const void* qc, int64_t ldq, int n_q, const void* w, void* cache, const int* cache_lens, const int* slots, int B,
+                     int rank, int R, float eps, int dt, cudaStream_t s) {
+  if (B == 0) return 0;
+  RB_DISPATCH_T(dt, (latent_append_kernel<T><<<RB_CEIL_DIV(B, 4), 128, 0, s>>>((const T*)qc, ldq, n_q, (const T*)w, (T*)cache, cache_lens,
+                                                                                  slots, B, rank, R, eps)));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// qa, out: [H, B, rank] fp32.  part_acc [H, B, splits, rank], part_ml [H, B, splits, 2] (splits > 1).
+int rb_latent_decode_core(const float* qa, const void* cache, const int* cache_lens, const int* slots, float* out, float* part_acc,
+                          float* part_ml, int B, int H, int rank, int R, int window, int splits, int dt, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (rank > kMaxRank || splits < 1 || (splits > 1 && (part_acc == nullptr || part_ml == nullptr))) return 1;
+  const int RP = ((rank + 3) & ~3) + 4;
+  const size_t smem = ((size_t)(kHT + kKT) * RP + kKT * kHT + kHT) * sizeof(float);
+  dim3 grid((unsigned)B, (unsigned)RB_CEIL_DIV(H, kHT), (unsigned)splits);
+  RB_DISPATCH_T(dt, {
+    auto kern = latent_decode_core_kernel<T>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+    kern<<<grid, kCT, smem, s>>>(qa, (const T*)cache, cache_lens, slots, out, part_acc, part_ml, B, H, rank, R, window, splits);
+  });
+  if (cudaGetLastError() != cudaSuccess) return 2;
+  if (splits > 1) {
+    latent_decode_combine_kernel<<<(unsigned)(H * B), 128, 0, s>>>(part_acc, part_ml, out, rank, splits);
+    if (cudaGetLastError() != cudaSuccess) return 2;
+  }
+  return 0;
 }
 
 }  // extern "C"

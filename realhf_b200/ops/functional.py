@@ -588,6 +588,23 @@ def group_rmsnorm_ref(x, w, groups: int, eps: float):
     return p.reshape(shp) * w.float()
 
 
+def cached_on(t: torch.Tensor, name: str, build):
+    """A tensor derived from weight `t` (a transposed or up-cast copy a kernel wants), kept as an attribute of `t` itself and
+    rebuilt when `t` was written in place or re-pointed at other storage.  Living on the tensor object, it can never be handed
+    to another weight that happens to reuse a freed address."""
+    tag = (t.data_ptr(), t._version)
+    hit = getattr(t, name, None)
+    if hit is None or hit[0] != tag:
+        hit = (tag, build(t.detach()))
+        setattr(t, name, hit)
+    return hit[1]
+
+
+def _tap_major(conv_w):
+    """[W, taps] (the parameter's layout) -> contiguous [taps, W] for the kernels."""
+    return None if conv_w is None else cached_on(conv_w, "_tap_major", lambda w: w.t().contiguous())
+
+
 def sublayer_input_ref(x, w, groups, eps, conv_w, pos, out_dtype, state=None, tok_slot=None, remain=None):
     n = group_rmsnorm_ref(x, w, groups, eps)
     h = n
@@ -615,7 +632,7 @@ def sublayer_input(x, w, groups: int, eps: float, conv_w, pos, out_dtype, state=
     being the number of tokens that follow t in its sequence."""
     if use_native(x):
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        lib().sublayer_input(x.contiguous(), w, conv_w, pos, out, state if conv_w is not None else None,
+        lib().sublayer_input(x.contiguous(), w, _tap_major(conv_w), pos, out, state if conv_w is not None else None,
                              tok_slot if state is not None else None, remain if state is not None else None, groups, eps)
         return out
     return sublayer_input_ref(x, w, groups, eps, conv_w, pos, out_dtype, state, tok_slot, remain)
@@ -639,7 +656,7 @@ def sublayer_input_step(x, w, groups: int, eps: float, conv_w, state, slots, out
     oldest first), which is then shifted by one with this token's n appended.  slots None = row b uses slot b."""
     if use_native(x):
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        lib().sublayer_input_step(x.contiguous(), w, conv_w, out, state if conv_w is not None else None, slots, groups, eps)
+        lib().sublayer_input_step(x.contiguous(), w, _tap_major(conv_w), out, state if conv_w is not None else None, slots, groups, eps)
         return out
     return sublayer_input_step_ref(x, w, groups, eps, conv_w, state, slots, out_dtype)
 

@@ -233,6 +233,30 @@ def test_latent_decode_attention_ring(device, dtype, H, qk, vd, rank, window, R)
     assert worst < (2e-5 if dtype == torch.float32 else 0.03)
 
 
+@pytest.mark.parametrize("device,dtype", ALL)
+@pytest.mark.parametrize("H,window,R,ctx", [(3, None, 256, 200), (20, 130, 256, 700), (1, 192, 192, 191), (17, 64, 128, 64)])
+def test_latent_decode_long_context_key_splits_and_head_tiles(device, dtype, H, window, R, ctx):
+    """One step at a long context straight from a filled ring (positions beyond R have wrapped): on CUDA several key splits per
+    row, split partials merged, more heads than one head tile."""
+    g = torch.Generator().manual_seed(H)
+    B, qk, vd, rank = 2, 8, 8, 40
+    w_ukv = (torch.randn(H * (qk + vd), rank, generator=g) / math.sqrt(rank)).to(dtype)
+    lat = torch.randn(B, ctx + 1, rank, generator=g).to(dtype)            # latents of positions 0 .. ctx (the new token included)
+    cache = torch.zeros(B, R, rank, dtype=dtype)
+    for p_ in range(max(0, ctx + 1 - R), ctx + 1):
+        cache[:, p_ % R] = lat[:, p_]
+    q = (torch.randn(B, H * qk, generator=g) * 2).to(dtype)
+    lens = torch.full((B,), ctx, dtype=torch.int32, device=device)
+    got = A.latent_decode_attention(q.to(device), None, w_ukv.to(device), cache.to(device), lens, None, H, qk, vd, 0.3, window, 1e-5)
+    for b in range(B):
+        kvb = lat[b].double() @ w_ukv.double().t()
+        kh = kvb[:, : H * qk].view(ctx + 1, H, qk)
+        vh = kvb[:, H * qk:].view(ctx + 1, H, vd)
+        lo = 0 if window is None else max(0, ctx - window + 1)
+        want = torch.stack([torch.softmax((kh[lo:, h] @ q[b].double().view(H, qk)[h]) * 0.3, 0) @ vh[lo:, h] for h in range(H)]).reshape(1, -1)
+        assert rel_err(got[b:b + 1], want) < (2e-5 if dtype == torch.float32 else 0.03), b
+
+
 @pytest.mark.parametrize("device,dtype", EXACT)
 def test_window_edge_in_decode_one_key_stands_out(device, dtype):
     H, qk, vd, rank, window = 1, 4, 4, 4, 5
