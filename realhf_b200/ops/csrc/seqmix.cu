@@ -135,6 +135,66 @@ __global__ void __launch_bounds__(kThreads) sublayer_input_kernel(
   }
 }
 
+// Packed form, token-tiled: a CTA owns kTT consecutive packed tokens x a chunk of groups.  The tile's rows and the taps - 1
+// rows before it are staged once in shared memory (raw fp32), every (row, group) root mean square is reduced from there by one
+// warp, and each thread then produces its 4 channels for all tokens of the tile with the norm and tap weights in registers: a
+// row of x is read once per tile instead of once per tap.  Same arithmetic, in the same order per element, as the row kernel.
+constexpr int kTT = 8;
+
+__global__ void __launch_bounds__(kThreads) sublayer_input_tiled_kernel(
+    const void* __restrict__ x, int dtx, const void* __restrict__ w, const void* __restrict__ cw, int dta, void* __restrict__ out, int dto,
+    const int* __restrict__ pos, float* __restrict__ state, const int* __restrict__ tok_slot, const int* __restrict__ remain,
+    int64_t n_tok, int W, int groups, int gpb, int taps, float eps) {
+  extern __shared__ float sm[];
+  const int g0 = blockIdx.y * gpb, ng = min(gpb, groups - g0), gs = W / groups;
+  const int E = ng * gs, e0 = g0 * gs;
+  const int halo = taps - 1, n_rows = kTT + halo;
+  float* raw = sm;                           // [n_rows][E]
+  float* rstd = sm + (size_t)n_rows * gpb * gs;   // [n_rows][ng]
+  const int64_t t0 = (int64_t)blockIdx.x * kTT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int q = threadIdx.x; q < n_rows * (E / 4); q += blockDim.x) {
+    const int r = q / (E / 4), c = (q - r * (E / 4)) * 4;
+    const int64_t t = t0 - halo + r;
+    const float4 v = (t >= 0 && t < n_tok) ? ld4_any(x, dtx, t * (int64_t)W + e0 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(raw + (size_t)r * E + c) = v;
+  }
+  __syncthreads();
+  for (int pair = warp; pair < n_rows * ng; pair += nwarp) {
+    const int r = pair / ng, g = pair - r * ng;
+    const float* src = raw + (size_t)r * E + g * gs;
+    float s = 0.f;
+    for (int e = lane * 4; e < gs; e += 128) { const float4 v = *reinterpret_cast<const float4*>(src + e); s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+    s = rb::warp_sum(s);
+    if (lane == 0) rstd[pair] = 1.f / sqrtf(s / (float)gs + eps);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x * 4; c < E; c += blockDim.x * 4) {
+    const int g = c / gs, e = e0 + c;
+    const float4 we = ld4_any(w, dta, e);
+    float4 cwj[kMaxTaps];
+    for (int j = 0; j < taps; ++j) cwj[j] = ld4_any(cw, dta, (int64_t)j * W + e);
+    for (int i = 0; i < kTT; ++i) {
+      const int64_t t = t0 + i;
+      if (t >= n_tok) break;
+      const int row = i + halo, p = pos[t];
+      const float4 n_t = mul4(scl4(*reinterpret_cast<const float4*>(raw + (size_t)row * E + c), rstd[row * ng + g]), we);
+      float4 h = fma4(cwj[taps - 1], n_t, n_t);
+      for (int r = 0; r < taps - 1; ++r) {
+        const int back = taps - 1 - r;
+        if (p < back) continue;
+        const float4 n_r = mul4(scl4(*reinterpret_cast<const float4*>(raw + (size_t)(row - back) * E + c), rstd[(row - back) * ng + g]), we);
+        h = fma4(cwj[r], n_r, h);
+      }
+      if (state != nullptr) {
+        const int slot = tok_slot[t], rem = remain[t];
+        if (slot >= 0 && rem < taps - 1) *reinterpret_cast<float4*>(state + ((int64_t)slot * (taps - 1) + (taps - 2 - rem)) * W + e) = n_t;
+      }
+      st4_any(out, dto, t * (int64_t)W + e, h);
+    }
+  }
+}
+
 // One-token form: the earlier inputs are state[slot] ([taps - 1, W], oldest first), shifted by one afterwards.
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads) sublayer_input_step_kernel(
@@ -274,6 +334,21 @@ int rb_sublayer_input(const void* x, int dtx, const void* w, const void* cw, int
   if (smem > 48 * 1024) return 1;
   const bool vec = (W / groups) % 4 == 0 && aligned16(x) && aligned16(w) && aligned16(out) && (state == nullptr || aligned16(state)) &&
                    (cw == nullptr || aligned16(cw));
+  if (vec && taps > 1 && rows >= 4 * kTT * rb::kNumSMs) {   // long packed batches: token tiles (each row of x is read once per tile)
+    int gt = std::max(1, std::min(groups, 1024 / std::max(W / groups, 1)));
+    const size_t smem_t = (size_t)(kTT + taps - 1) * gt * ((size_t)(W / groups) + 1) * sizeof(float);
+    if (smem_t <= 100 * 1024) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        if (cudaFuncSetAttribute(sublayer_input_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess) return 2;
+        attr_set = true;
+      }
+      dim3 grid_t((unsigned)RB_CEIL_DIV(rows, (int64_t)kTT), (unsigned)RB_CEIL_DIV(groups, gt));
+      sublayer_input_tiled_kernel<<<grid_t, kThreads, smem_t, s>>>(x, dtx, w, cw, dta, out, dto, pos, state, tok_slot, remain, rows, W, groups,
+                                                                   gt, taps, eps);
+      return cudaGetLastError() == cudaSuccess ? 0 : 2;
+    }
+  }
   dim3 grid((unsigned)rows, (unsigned)RB_CEIL_DIV(groups, gpb));
   auto kern = vec ? sublayer_input_kernel<true> : sublayer_input_kernel<false>;
   kern<<<grid, kThreads, smem, s>>>(x, dtx, w, cw, dta, out, dto, pos, state, tok_slot, remain, W, groups, gpb, taps, eps);

@@ -112,6 +112,40 @@ def test_sublayer_input_packed_and_step(device, dtype, W, groups, taps):
 
 
 @pytest.mark.parametrize("device,dtype", ALL)
+@pytest.mark.parametrize("W,groups,taps", [(64, 4, 4), (96, 1, 2), (32, 8, 5)])
+def test_sublayer_input_long_packed_batch(device, dtype, W, groups, taps):
+    """Thousands of packed tokens (on CUDA the token-tiled kernel): sequences that start and end inside, at the first and at the
+    last row of a tile, and the state every sequence leaves behind."""
+    g = torch.Generator().manual_seed(taps)
+    lens = [1, 7, 8, 9, 2, 1, 1500, 3, 16, 1700, 5, 24, 1, 1800, 2, 40]
+    T = sum(lens)
+    x = torch.randn(T, W, generator=g) * 2
+    w = (1 + 0.3 * torch.randn(W, generator=g)).to(dtype)
+    cw = (0.5 * torch.randn(W, taps, generator=g)).to(dtype)
+    nrm = O.grouped_rms_norm(x, w, groups, 1e-5)
+    want = nrm.clone()
+    pos = torch.cat([torch.arange(n) for n in lens])
+    for j in range(taps):
+        back = taps - 1 - j
+        src = torch.zeros_like(nrm)
+        src[back:] = nrm[: T - back] if back else nrm
+        want += torch.where((pos >= back).unsqueeze(-1), src, torch.zeros_like(src)) * cw[:, j].double()
+    from realhf_b200.models.hetero_block import packed_meta
+    slots = torch.randperm(len(lens), generator=g).int().to(device)
+    meta = packed_meta(torch.tensor([0] + lens).cumsum(0).int().to(device), T, slots)
+    state = torch.zeros(len(lens), taps - 1, W, device=device)
+    got = OF.sublayer_input(x.to(device), w.to(device), groups, 1e-5, cw.to(device), meta.pos, dtype, state, meta.tok_slot, meta.remain)
+    assert rel_err(got, want) < (1e-5 if dtype == torch.float32 else 0.02)
+    off = 0
+    for b, n in enumerate(lens):
+        tail = torch.zeros(taps - 1, W, dtype=torch.float64)
+        k = min(n, taps - 1)
+        tail[taps - 1 - k:] = nrm[off + n - k: off + n]
+        assert torch.allclose(state[int(slots[b])].double().cpu(), tail, atol=1e-5), (b, n)
+        off += n
+
+
+@pytest.mark.parametrize("device,dtype", ALL)
 def test_residual_add_norm_clamped_glu_softcap(device, dtype):
     g = torch.Generator().manual_seed(5)
     x = torch.randn(7, 36, generator=g)
