@@ -2,8 +2,8 @@
 roofline position of its kernels next to the like kernels of that model.  Reached through `bench.py --serve-bench rapodra`
 (the default workload of bench.py is unaffected).
 
-Both models run through `models.generation.generate` (packed prefill into the decode state, CUDA-graph decode with the sampler
-in the graph), random weights, bf16.  Timing: CUDA events, >= 3 warm-up calls, weights + state far larger than L2 per call for
+Both models run through `models.generation`: prefill = `prefill_into_state` (the packed prefill `generate` performs) into a
+standing decode state, decode = the CUDA-graph loop of `generate` with the sampler in the graph; random weights, bf16.  Timing: CUDA events, >= 3 warm-up calls, weights + state far larger than L2 per call for
 the model-level numbers; the kernel table flushes L2 (a 256 MB write) between timed launches.  One JSON line per result.
 """
 
@@ -80,11 +80,26 @@ def model_numbers(name: str, s: dict, n_layers: int, batch: int, prompt_len: int
     ids = torch.randint(3, s["vocab"], (batch * prompt_len,), device=dev)
     cu = torch.arange(0, batch + 1, device=dev, dtype=torch.int32) * prompt_len
     for label, m in (("rapodra", new), ("llama-equal-size", old)):
+        # prefill: the packed prefill into a standing decode state (`prefill_into_state`, what `generate` calls), so that the
+        # number is the model's and not the caching allocator's (a fresh multi-GB state per `generate` call can fall into
+        # cudaMalloc inside the timed region); decode: the CUDA-graph loop of `generate`
+        st = gen.DecodeState(m, batch, prompt_len + new_tokens)
         pre, dec = [], []
+        with torch.no_grad():
+            for it in range(7):
+                st.free_slots = list(range(batch))
+                slots = st.alloc(batch)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                gen.prefill_into_state(m, st, slots, ids, cu, prompt_len)
+                b.record()
+                torch.cuda.synchronize()
+                if it >= 2:
+                    pre.append(a.elapsed_time(b))
+        del st
         for it in range(4):
             gen.generate(m, ids, cu, g, eos_id=None, pad_id=0)
             if it:                                     # first call: lazy initialisation
-                pre.append(gen.LAST_TIMING["prefill_ms"])
                 dec.append(gen.LAST_TIMING["ms_per_decode_step"])
         pre_ms, dec_ms = sorted(pre)[len(pre) // 2], sorted(dec)[len(dec) // 2]
         out.append(dict(bench="serve", size=name, model=label, layers=n_layers, batch=batch, prompt_len=prompt_len, new_tokens=new_tokens,

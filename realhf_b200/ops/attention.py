@@ -246,7 +246,14 @@ def latent_window_attention(q, kv, pos, n_heads: int, qk: int, vd: int, scale: f
             vv = kv[:, n_heads * qk:].view(T, n_heads, vd)
             out = lib().attn_fwd_window(qv, kk, vv, cu_seqlens, max_seqlen, scale, True, window if window is not None else 0)[0]
             return out.view(T, n_heads * vd)
-        return lib().latent_window_attention(q, kv, pos, n_heads, qk, vd, scale, window if window is not None else 0)
+        if vd <= 256 and (16 * qk + 32 * (qk + 1) + 32 * vd + 512) * 4 <= 200 * 1024:
+            return lib().latent_window_attention(q, kv, pos, n_heads, qk, vd, scale, window if window is not None else 0)
+        # head dims beyond the kernel's shared-memory tiles: the reference formula on the device, sequence by sequence
+        out = torch.empty(q.shape[0], n_heads * vd, dtype=q.dtype, device=q.device)
+        starts = torch.nonzero(pos == 0).flatten().tolist() + [q.shape[0]]
+        for a, b in zip(starts[:-1], starts[1:]):
+            out[a:b] = latent_window_attention_ref(q[a:b], kv[a:b], pos[a:b], n_heads, qk, vd, scale, window)
+        return out
     return latent_window_attention_ref(q, kv, pos, n_heads, qk, vd, scale, window)
 
 
@@ -296,7 +303,9 @@ def latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads: 
     over the cached latents of the window, and W_uv is applied to the result.  Does not advance cache_lens."""
     if use_native(qc):
         rank, R, B = cache.shape[2], cache.shape[1], qc.shape[0]
-        if os.environ.get("REAL_LATENT_DECODE", "split") == "fused" or rank > 512:
+        if rank > 512:  # beyond both kernels' register / shared-memory tiles: the reference formula on the device
+            return latent_decode_attention_ref(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale, window, eps)
+        if os.environ.get("REAL_LATENT_DECODE", "split") == "fused":
             # one launch per (row, head): small problems / A-B runs
             return lib().latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale,
                                                  window if window is not None else 0, eps)

@@ -252,11 +252,25 @@ __global__ void __launch_bounds__(kDT) latent_decode_attention_kernel(
 // batched matrix product ([H, B, rank] fp32); `latent_decode_core` below turns (qa, cached latents) into the softmax-weighted
 // latent sums [H, B, rank] fp32, to which the caller applies W_uv.
 //
-// Core: one CTA per (row, tile of 16 heads, key split), 128 threads.  A tile of 32 latent rows is staged in shared memory as
-// fp32 and used twice: scores S[16 heads][32 keys] (thread = 1 key x 4 heads, the dot over the rank with 16-byte shared loads;
+// Core: one CTA per (row, tile of 16 heads, key split), 128 threads.  A tile of 32 latent rows is staged in shared memory in
+// the cache's own type and used twice: scores S[16 heads][32 keys] (thread = 1 key x 4 heads, the dot over the rank with 16-byte shared loads;
 // the qa reads are warp broadcasts) and, after an online-softmax update per head, the weighted sum into the thread's
 // 16 heads x 4 rank columns of accumulators.  With more than one split the partial (max, sum, accumulator) triples go to a
 // workspace and `latent_decode_combine` merges them.
+// 4 consecutive elements of a shared-memory row as fp32 (the row keeps the cache's storage type: half the bytes of an fp32
+// tile for 16-bit caches, so three CTAs fit an SM)
+RB_DEVICE float4 ld4s(const float* p) { return *reinterpret_cast<const float4*>(p); }
+RB_DEVICE float4 ld4s(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+RB_DEVICE float4 ld4s(const __half* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __half2 a = *reinterpret_cast<const __half2*>(&raw.x), b = *reinterpret_cast<const __half2*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
 constexpr int kCT = 128;     // threads
 constexpr int kHT = 16;      // heads per CTA
 constexpr int kKT = 32;      // keys per tile
@@ -289,8 +303,8 @@ __global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __
   extern __shared__ float sm[];
   const int RP = ((rank + 3) & ~3) + 4;        // padded row: 16-byte aligned, rows 4 banks apart
   float* qs = sm;                              // [kHT][RP]
-  float* cs = qs + kHT * RP;                   // [kKT][RP]
-  float* ps = cs + kKT * RP;                   // [kKT][kHT]  scores, then softmax weights
+  T* cs = reinterpret_cast<T*>(qs + kHT * RP); // [kKT][RP]   latent rows as stored
+  float* ps = reinterpret_cast<float*>(cs + kKT * RP);   // [kKT][kHT]  scores, then softmax weights
   float* al = ps + kKT * kHT;                  // [kHT] rescale factor of the running sums for this tile
   const int tid = threadIdx.x;
   const int b = blockIdx.x, h0 = blockIdx.y * kHT, split = blockIdx.z;
@@ -307,7 +321,7 @@ __global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __
   }
   const bool vec = rank % (16 / (int)sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0;
   if (vec)                                     // the vector fill writes columns [0, rank) only
-    for (int e = tid; e < kKT * (RP - rank); e += kCT) cs[(e / (RP - rank)) * RP + rank + e % (RP - rank)] = 0.f;
+    for (int e = tid; e < kKT * (RP - rank); e += kCT) cs[(e / (RP - rank)) * RP + rank + e % (RP - rank)] = rb::from_f<T>(0.f);
   const int my_k = tid & 31, hg = tid >> 5;    // scores: key my_k of the tile, heads 4 hg .. 4 hg + 3
   const int r0 = tid * 4;                      // sums: rank columns r0 .. r0 + 3 of all 16 heads
   float acc[kHT][4];
@@ -320,37 +334,31 @@ __global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __
     const int nk = min(kKT, k_end - kb);
     __syncthreads();                           // previous tile fully consumed (and qs written, first time round)
     if (vec) {
-      // 16-byte global loads: VPT elements per thread and step; the pad columns beyond the rank stay zero from the first fill
+      // 16-byte global loads: VPT elements per thread and step, stored as two 8-byte halves (rows are 8-byte aligned); the pad
+      // columns beyond the rank stay zero from the first fill
       constexpr int VPT = 16 / sizeof(T);
       const int per_row = rank / VPT;
       for (int e = tid; e < kKT * per_row; e += kCT) {
         const int k = e / per_row, v = e - k * per_row;
-        float f[VPT];
-        if (k < nk) {
-          const rb::Pack<T, VPT> pk = *reinterpret_cast<const rb::Pack<T, VPT>*>(cache + (slot * R + ((kb + k) % R)) * (int64_t)rank + v * VPT);
-#pragma unroll
-          for (int i = 0; i < VPT; ++i) f[i] = rb::to_f(pk.v[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < VPT; ++i) f[i] = 0.f;
-        }
-        float4* dst = reinterpret_cast<float4*>(cs + k * RP + v * VPT);
-#pragma unroll
-        for (int i = 0; i < VPT / 4; ++i) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (k < nk) raw = *reinterpret_cast<const uint4*>(cache + (slot * R + ((kb + k) % R)) * (int64_t)rank + v * VPT);
+        uint2* dst = reinterpret_cast<uint2*>(cs + k * RP + v * VPT);
+        dst[0] = make_uint2(raw.x, raw.y);
+        dst[1] = make_uint2(raw.z, raw.w);
       }
     } else {
       for (int e = tid; e < kKT * RP; e += kCT) {
         const int k = e / RP, r = e % RP;
-        cs[e] = (k < nk && r < rank) ? rb::to_f(cache[(slot * R + ((kb + k) % R)) * (int64_t)rank + r]) : 0.f;
+        cs[e] = (k < nk && r < rank) ? cache[(slot * R + ((kb + k) % R)) * (int64_t)rank + r] : rb::from_f<T>(0.f);
       }
     }
     __syncthreads();
     {
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
-      const float4* cr = reinterpret_cast<const float4*>(cs + my_k * RP);
+      const T* cr = cs + my_k * RP;
 #pragma unroll 4
       for (int r4 = 0; r4 < (RP - 4) / 4; ++r4) {
-        const float4 cv = cr[r4];
+        const float4 cv = ld4s(cr + 4 * r4);
 #pragma unroll
         for (int hh = 0; hh < 4; ++hh) {
           const float4 qv = reinterpret_cast<const float4*>(qs + (hg * 4 + hh) * RP)[r4];
@@ -384,7 +392,7 @@ __global__ void __launch_bounds__(kCT) latent_decode_core_kernel(const float* __
         for (int i = 0; i < 4; ++i) acc[h][i] *= a;
       }
       for (int k = 0; k < nk; ++k) {
-        const float4 cv = *reinterpret_cast<const float4*>(cs + k * RP + r0);
+        const float4 cv = ld4s(cs + k * RP + r0);
         const float4* pk = reinterpret_cast<const float4*>(ps + k * kHT);
 #pragma unroll
         for (int h4 = 0; h4 < kHT / 4; ++h4) {
@@ -522,7 +530,8 @@ int rb_latent_decode_core(const float* qa, const void* cache, const int* cache_l
   if (B == 0) return 0;
   if (rank > kMaxRank || splits < 1 || (splits > 1 && (part_acc == nullptr || part_ml == nullptr))) return 1;
   const int RP = ((rank + 3) & ~3) + 4;
-  const size_t smem = ((size_t)(kHT + kKT) * RP + kKT * kHT + kHT) * sizeof(float);
+  const size_t esz = dt == 0 ? 4 : 2;
+  const size_t smem = ((size_t)kHT * RP + kKT * kHT + kHT) * sizeof(float) + (size_t)kKT * RP * esz;
   dim3 grid((unsigned)B, (unsigned)RB_CEIL_DIV(H, kHT), (unsigned)splits);
   RB_DISPATCH_T(dt, {
     auto kern = latent_decode_core_kernel<T>;

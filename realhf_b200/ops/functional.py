@@ -630,7 +630,7 @@ def sublayer_input(x, w, groups: int, eps: float, conv_w, pos, out_dtype, state=
     h = n.  With `state` [n_slots, taps - 1, W] fp32, the n of the last taps - 1 tokens of every sequence is left in
     state[tok_slot[t]] (oldest first; rows of a shorter sequence are not written, the slot manager zeroes them), `remain[t]`
     being the number of tokens that follow t in its sequence."""
-    if use_native(x):
+    if use_native(x) and (conv_w is None or conv_w.shape[1] <= 8) and groups * 32 <= 48 * 1024:   # the kernels hold <= 8 taps
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         lib().sublayer_input(x.contiguous(), w, _tap_major(conv_w), pos, out, state if conv_w is not None else None,
                              tok_slot if state is not None else None, remain if state is not None else None, groups, eps)
@@ -654,7 +654,7 @@ def sublayer_input_step_ref(x, w, groups, eps, conv_w, state, slots, out_dtype):
 def sublayer_input_step(x, w, groups: int, eps: float, conv_w, state, slots, out_dtype):
     """Decode form of `sublayer_input` (one token per row): the earlier inputs come from state[slots[b]] ([taps - 1, W] fp32,
     oldest first), which is then shifted by one with this token's n appended.  slots None = row b uses slot b."""
-    if use_native(x):
+    if use_native(x) and (conv_w is None or conv_w.shape[1] <= 8) and groups * 32 <= 48 * 1024:
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         lib().sublayer_input_step(x.contiguous(), w, _tap_major(conv_w), out, state if conv_w is not None else None, slots, groups, eps)
         return out
