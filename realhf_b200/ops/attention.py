@@ -314,9 +314,10 @@ def latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads: 
             lib().latent_append(qc, n_q, w_ln, cache, cache_lens, slots, eps)
         wk, wv = _absorbed_projections(w_ukv, n_heads, qk, vd, scale)
         qa = torch.bmm(qc[:, :n_q].reshape(B, n_heads, qk).transpose(0, 1).float(), wk)           # [H, B, rank] fp32
-        # enough CTAs to fill the GPU: split the keys when rows x head tiles are few (a split is at least two 32-key tiles)
+        # enough CTAs to fill the GPU (three fit an SM): split the keys when rows x head tiles are few; a split is at least two
+        # 32-key tiles
         ctas = B * ((n_heads + 15) // 16)
-        splits = max(1, min((2 * 148 + ctas - 1) // ctas, R // 64, 32))
+        splits = max(1, min((3 * 148 + ctas - 1) // ctas, R // 64, 32))
         o = lib().latent_decode_core(qa, cache, cache_lens, slots, window if window is not None else 0, splits)
         return torch.bmm(o, wv).transpose(0, 1).reshape(B, n_heads * vd).to(qc.dtype)
     return latent_decode_attention_ref(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale, window, eps)
