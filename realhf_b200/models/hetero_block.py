@@ -56,7 +56,7 @@ def _mlp(model, i: int, h: torch.Tensor, mcfg) -> torch.Tensor:
     if mcfg.kind == "moe":
         from realhf_b200.models import moe
         return moe.moe_forward(model, i, h, mcfg.moe)
-    a = OF.clamped_glu(OF.linear(h, p[f"{i}.mlp.gate_up.weight"]), mcfg.limit, mcfg.alpha)
+    a = OF.clamped_gated_linear(h, p[f"{i}.mlp.gate_up.weight"], mcfg.limit, mcfg.alpha)
     return OF.linear(a, p[f"{i}.mlp.down.weight"])
 
 

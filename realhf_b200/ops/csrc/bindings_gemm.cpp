@@ -239,7 +239,25 @@ std::vector<Tensor> gemm_glu(const Tensor& x, const Tensor& w, int64_t act_kind,
   return {act};
 }
 
+extern "C" int rb_gemm_2cta_glu_ex(const void* A, const void* B, void* act, void* raw, int M, int F, int K, int64_t lda, int64_t ldb,
+                                   int64_t ld_act, int64_t ld_raw, int in_dt, int act_kind, float limit, float alpha, int num_sms, cudaStream_t s);
+
+// min(g, L) * sigmoid(alpha min(g, L)) * (clamp(u, -L, L) + 1) in the epilogue of the fused [gate; up] projection (inference form)
+Tensor gemm_glu_clamped(const Tensor& x, const Tensor& w, double limit, double alpha, int64_t num_sms) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && w.size(0) % 2 == 0 && w.size(1) == x.size(1));
+  TORCH_CHECK(x.scalar_type() == w.scalar_type() && (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf));
+  const int64_t M = x.size(0), K = x.size(1), F = w.size(0) / 2;
+  c10::cuda::CUDAGuard g(x.device());
+  auto act = at::empty({M, F}, x.options());
+  int rc = rb_gemm_2cta_glu_ex(x.data_ptr(), w.data_ptr(), act.data_ptr(), nullptr, (int)M, (int)F, (int)K, x.stride(0), w.stride(0), F, 2 * F,
+                               x.scalar_type() == at::kBFloat16 ? 1 : 2, 2, (float)limit, (float)alpha, (int)num_sms,
+                               at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "gemm_glu_clamped failed: ", rc);
+  return act;
+}
+
 void register_gemm_ops(torch::Library& m) {
+  m.def("gemm_glu_clamped(Tensor x, Tensor w, float limit, float alpha, int num_sms) -> Tensor", &gemm_glu_clamped);
   m.def("gemm_glu(Tensor x, Tensor w, int act_kind, bool want_raw, int num_sms) -> Tensor[]", &gemm_glu);
   m.def("gemm_grouped_wgrad(Tensor dy, Tensor x, Tensor(a!) out, Tensor offsets, bool accumulate, int num_sms) -> ()", &gemm_grouped_wgrad);
   m.def("gemm_grouped(Tensor a, Tensor w, Tensor offsets, bool b_mn, int num_sms) -> Tensor", &gemm_grouped);

@@ -245,7 +245,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_2cta_kernel(const __grid_con
               // the unfused path rounds gate / up to the activation dtype before the nonlinearity: do the same, so that the saved
               // raw projections (backward) and the activation are consistent
               const float gr = rb::to_f(rb::from_f<OutT>(g[i])), ur = rb::to_f(rb::from_f<OutT>(u[i]));
-              v[i] = glu_act_fwd(gr, p.glu_act) * ur;
+              if (p.glu_act == 2) {
+                const float gc = fminf(gr, p.glu_limit), uc = fminf(fmaxf(ur, -p.glu_limit), p.glu_limit);
+                v[i] = gc / (1.f + __expf(-p.glu_alpha * gc)) * (uc + 1.f);
+              } else {
+                v[i] = glu_act_fwd(gr, p.glu_act) * ur;
+              }
             }
             store_chunk<OutT>(Cp + (int64_t)row * p.ldc + col, v, n_valid, vec_ok);
             if (raw != nullptr) {
@@ -393,9 +398,9 @@ int rb_gemm_2cta_gated(const void* A, const void* B, void* C, const void* bias, 
 }
 
 // act[M, F] = glu(A[M,K] x [gate; up][2F, K]^T) with the activation in the epilogue; raw (optional) [M, 2F] receives gate | up.
-// in_dt: 1 bf16, 2 fp16 (outputs use the same dtype).  act_kind: 0 silu, 1 gelu-tanh.
-int rb_gemm_2cta_glu(const void* A, const void* B, void* act, void* raw, int M, int F, int K, int64_t lda, int64_t ldb, int64_t ld_act,
-                     int64_t ld_raw, int in_dt, int act_kind, int num_sms, cudaStream_t s) {
+// in_dt: 1 bf16, 2 fp16 (outputs use the same dtype).  act_kind: 0 silu, 1 gelu-tanh, 2 clamped (with `limit`, `alpha`).
+int rb_gemm_2cta_glu_ex(const void* A, const void* B, void* act, void* raw, int M, int F, int K, int64_t lda, int64_t ldb, int64_t ld_act,
+                        int64_t ld_raw, int in_dt, int act_kind, float limit, float alpha, int num_sms, cudaStream_t s) {
   if (M <= 0 || F <= 0 || K <= 0) return 0;
   if (in_dt != 1 && in_dt != 2) return -10;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -11;
@@ -405,9 +410,14 @@ int rb_gemm_2cta_glu(const void* A, const void* B, void* act, void* raw, int M, 
   bool ok = make_tmap(&ta, A, bf, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BK, (uint32_t)BM);
   ok = ok && make_tmap(&tb, B, bf, (uint64_t)(2 * F), (uint64_t)K, (uint64_t)ldb, BK, 128);
   if (!ok) return -13;
-  Params p{act, nullptr, ld_act, M, F, K, 0, nullptr, 0, 1, 0, nullptr, F, act_kind, raw, ld_raw};
+  Params p{act, nullptr, ld_act, M, F, K, 0, nullptr, 0, 1, 0, nullptr, F, act_kind, raw, ld_raw, limit, alpha};
   if (in_dt == 1) return launch2<256, false, false, __nv_bfloat16, 1, true>(ta, tb, p, num_sms, s);
   return launch2<256, false, false, __half, 0, true>(ta, tb, p, num_sms, s);
+}
+
+int rb_gemm_2cta_glu(const void* A, const void* B, void* act, void* raw, int M, int F, int K, int64_t lda, int64_t ldb, int64_t ld_act,
+                     int64_t ld_raw, int in_dt, int act_kind, int num_sms, cudaStream_t s) {
+  return rb_gemm_2cta_glu_ex(A, B, act, raw, M, F, K, lda, ldb, ld_act, ld_raw, in_dt, act_kind, 0.f, 0.f, num_sms, s);
 }
 
 }  // extern "C"

@@ -31,9 +31,11 @@ struct Params {
   // optional gated-linear-unit epilogue (2-CTA kernel): B is the fused [gate; up] weight with glu_F rows each, N = glu_F output
   // columns act(gate) * up are written to C, and (when glu_raw != nullptr) the raw gate | up projections to glu_raw [M, 2 glu_F]
   int glu_F;
-  int glu_act;       // 0 silu, 1 gelu (tanh approximation)
+  int glu_act;       // 0 silu, 1 gelu (tanh approximation), 2 clamped: min(g, L) * sigmoid(alpha min(g, L)) * (clamp(u, -L, L) + 1)
   void* glu_raw;
   int64_t ld_raw;
+  float glu_limit;   // L and alpha of the clamped form
+  float glu_alpha;
 };
 
 template <typename T> RB_DEVICE void store_chunk(T* dst, const float* v, int n_valid, bool vec_ok);

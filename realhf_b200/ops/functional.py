@@ -684,6 +684,20 @@ def clamped_glu(gu, limit: float, alpha: float = 1.702):
     return clamped_glu_ref(gu, limit, alpha)
 
 
+def clamped_gated_linear(x, w_gate_up, limit: float, alpha: float = 1.702):
+    """clamped_glu(x @ [Wg; Wu]^T).  16-bit CUDA operands of more than 128 rows run projection and activation as ONE kernel (the
+    activation in the epilogue of the CTA-pair tcgen05 GEMM, like `gated_linear`); everything else composes the two ops."""
+    if use_native(x) and x.dtype in (torch.bfloat16, torch.float16) and gemm_impl() is not None:
+        from realhf_b200.ops import gemm as G
+        if gemm_impl() is G.linear and G.gated_linear_supported(x, w_gate_up):
+            x2 = x.reshape(-1, x.shape[-1])
+            if x2.stride(-1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+                x2 = x2.contiguous()
+            out = lib().gemm_glu_clamped(x2, w_gate_up, limit, alpha, G._sms(x.device))
+            return out.view(*x.shape[:-1], w_gate_up.shape[0] // 2)
+    return clamped_glu(linear(x, w_gate_up), limit, alpha)
+
+
 def softcap_logits(logits, cap: Optional[float]):
     """fp32 cap * tanh(logits / cap) (cap None: the fp32 logits)."""
     if cap is None:

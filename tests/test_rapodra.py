@@ -165,6 +165,20 @@ def test_residual_add_norm_clamped_glu_softcap(device, dtype):
     assert got.dtype == torch.float32 and rel_err(got, 30 * torch.tanh(lg.double() / 30)) < 1e-5
 
 
+@pytest.mark.parametrize("device,dtype", ALL)
+@pytest.mark.parametrize("T,W,F", [(300, 64, 96), (40, 64, 96), (513, 128, 264)])
+def test_clamped_gated_linear(device, dtype, T, W, F):
+    """Projection + clamped GLU; on CUDA, 16-bit inputs of more than 128 rows take the GEMM-epilogue form."""
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, W, generator=g).to(dtype)
+    w = (torch.randn(2 * F, W, generator=g) * 2 / math.sqrt(W)).to(dtype)
+    gu = (x.double() @ w.double().t()).to(dtype).double()          # the projection is rounded to the compute type first
+    gg, uu = gu[:, :F].clamp(max=1.25), gu[:, F:].clamp(-1.25, 1.25)
+    want = gg * torch.sigmoid(1.702 * gg) * (uu + 1)
+    got = OF.clamped_gated_linear(x.to(device), w.to(device), 1.25, 1.702)
+    assert rel_err(got, want) < (1e-4 if dtype == torch.float32 else 0.03)
+
+
 def _attn_inputs(T, H, qk, vd, seed, dtype):
     g = torch.Generator().manual_seed(seed)
     q = torch.randn(T, H * qk + 5, generator=g).to(dtype)        # wider than the queries: like the fused q|latent projection
