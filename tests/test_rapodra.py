@@ -480,3 +480,32 @@ def test_checkpoint_roundtrip_and_family_detection(tmp_path):
     assert set(back) == set(w) and all(torch.equal(back[k].to(w[k].dtype), w[k]) for k in w)
     seq = toks(20, cfg["vocab"], 3)
     assert rel_err(packed_logits(m.eval(), [seq]), O.forward(cfg, w, seq)) < 2e-4
+
+
+def test_family_through_registry_factory_backend_and_engine():
+    """The family as the rest of the framework reaches it: model registry -> `real_model` factory -> inference backend ->
+    `ReaLEngine.generate` / `forward` on a packed `SequenceSample`."""
+    import realhf_b200.engine.engine  # noqa: F401  (registers the backends)
+    import realhf_b200.models.factory  # noqa: F401  (registers `real_model`)
+    from realhf_b200.api import model as model_api
+    from realhf_b200.api.config import ModelAbstraction, ModelBackendAbstraction, ModelName
+    from realhf_b200.api.data import SequenceSample
+    from realhf_b200.api.model import FinetuneSpec
+    m = model_api.make_model(ModelAbstraction("real_model", args=dict(model_path="", is_critic=False, init_from_scratch=True, dtype="fp32",
+                                                                      hf_model_family="rapodra")), ModelName("actor", 0), "cpu")
+    assert m.module.config.blocks is not None and m.module.config.blocks[1].attn.kv_from == 0
+    m = model_api.make_backend(ModelBackendAbstraction("inference")).initialize(m, FinetuneSpec(1, 1, 1))
+    lens = [5, 9, 3]
+    ids = torch.randint(3, 100, (sum(lens),))
+    x = SequenceSample.from_default(seqlens=lens, ids=list(range(3)), data=dict(packed_input_ids=ids))
+    g = GenerationHyperparameters(max_new_tokens=6, min_new_tokens=6, greedy=True)
+    out = m.module.generate(x, m.tokenizer, g)[0]
+    assert tuple(out.tokens.shape) == (3, 6)
+    # the engine's greedy tokens are the argmax of a packed forward over prompt + generated tokens
+    seqs = [ids[a:b].tolist() + out.tokens[i].tolist() for i, (a, b) in enumerate(zip([0, 5, 14], [5, 14, 17]))]
+    lg = packed_logits(m.module.module, seqs)
+    off = 0
+    for i, s in enumerate(seqs):
+        pred = lg[off + lens[i] - 1: off + len(s) - 1].argmax(-1).tolist()
+        assert pred == out.tokens[i].tolist()
+        off += len(s)
