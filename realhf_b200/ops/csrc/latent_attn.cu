@@ -5,9 +5,12 @@
 //                            [T, rank] (input of the key/value up-projection GEMM) and into the ring cache of its sequence
 //   latent_window_attention  packed prefill over the up-projected keys / values: 16 queries x 1 head per CTA, key tiles staged
 //                            in shared memory, online softmax
-//   latent_decode_attention  one token per row, keys / values never formed: the query is multiplied into the latent space
-//                            (q W_uk), scores and the weighted sum run over the cached latents, W_uv is applied to the result;
-//                            a block that owns its latent also normalises and appends the new row
+//   decode (one token per row; keys / values are never formed: the query is multiplied into the latent space, q W_uk, scores and
+//   the weighted sum run over the cached latents, W_uv is applied to the result)
+//     split form (default): latent_append + latent_decode_core (+ latent_decode_combine); the two small per-head projections
+//                            are batched matrix products issued by the caller
+//     latent_decode_attention  the whole step in one launch per (row, head), a block that owns its latent also normalises
+//                            and appends the new row: small problems and A/B runs (`REAL_LATENT_DECODE=fused`)
 //
 // Scores, softmax and all accumulations are fp32; storage is T (bf16 / fp16 / fp32).  Compiled without fast-math.
 // The cache of a slot is a ring of R rows: position p lives in row p % R.

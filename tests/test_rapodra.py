@@ -254,10 +254,14 @@ def test_window_edge_in_prompt_one_key_stands_out(device, dtype):
 
 
 @pytest.mark.parametrize("device,dtype", ALL)
+@pytest.mark.parametrize("impl", ["split", "fused"])
 @pytest.mark.parametrize("H,qk,vd,rank,window,R", [(2, 16, 8, 24, 7, 7), (3, 8, 16, 40, 5, 11), (1, 32, 32, 16, None, 64), (2, 16, 24, 33, 1, 1)])
-def test_latent_decode_attention_ring(device, dtype, H, qk, vd, rank, window, R):
+def test_latent_decode_attention_ring(device, dtype, H, qk, vd, rank, window, R, impl, monkeypatch):
     """Token-by-token decode over a ring cache, rows in shuffled slots, one row appended per step by an owning block and read
-    back by a sharing block, against whole-sequence attention over up-projected keys / values."""
+    back by a sharing block, against whole-sequence attention over up-projected keys / values.  Both CUDA forms of the op."""
+    if impl == "fused" and device == "cpu":
+        pytest.skip("one reference on the CPU")
+    monkeypatch.setenv("REAL_LATENT_DECODE", impl)
     g = torch.Generator().manual_seed(rank)
     B, n = 3, 30
     w_ukv = (torch.randn(H * (qk + vd), rank, generator=g) / math.sqrt(rank)).to(dtype)
