@@ -294,3 +294,4 @@ register_hf_family(
         scale_attn_by_inverse_layer_idx=False, tied_embedding=True))
 
 from realhf_b200.api.from_hf import rapodra  # noqa: E402,F401  (registers the family)
+from realhf_b200.api.from_hf import tizodra  # noqa: E402,F401  (registers the family)

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import abc
 import dataclasses
-from typing import Any, Callable, Dict, List, Optional, Union
+from typing import Any, Callable, Dict, List, Optional, Tuple, Union
 
 import torch
 
@@ -75,11 +75,87 @@ class LatentAttentionConfig:
 
 
 @dataclasses.dataclass
+class WindowAttentionConfig:
+    """Softmax attention over cached keys / values with grouped key / value heads (query head h reads head h // (n_heads /
+    n_kv_heads)) and no rotation.  Every further mechanism is a switch or a constant, so that families can combine them:
+
+      * `window` / `keep_first`: query i sees key j <= i when i - j < window or j < keep_first (window None: all j <= i).  The
+        cache of a sequence is then `keep_first` fixed rows plus a ring of `window` rows, whatever the sequence's length;
+      * `value_norm`: every head's value is divided by its root mean square (no weight) before it is cached;
+      * `head_temp`: a learned per-head factor on the scaled score;
+      * `slope_base` b: the score loses slope_h * (i - j), slope_h = 2^(-b (h + 1) / n_heads) (None: no distance term);
+      * `sink`: a learned per-head logit added to the softmax denominator as exp(sink_h): a key-less, value-less entry;
+      * `out_gate`: head h's output is multiplied by sigmoid(w_g . x)_h, x being the mixer's input."""
+    n_heads: int
+    n_kv_heads: int
+    qk_dim: int
+    v_dim: int
+    scale: float
+    window: Optional[int] = None
+    keep_first: int = 0
+    qkv_bias: bool = True
+    value_norm: bool = True
+    head_temp: bool = True
+    slope_base: Optional[float] = 8.0
+    sink: bool = True
+    out_gate: bool = True
+
+    def __post_init__(self):
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if self.window is None:
+            self.keep_first = 0
+        elif self.window < 1 or self.keep_first < 0:
+            raise ValueError("window >= 1 and keep_first >= 0 expected")
+
+    def cache_rows(self, max_len: int) -> int:
+        """Rows a sequence of at most max_len tokens needs: position p lives in row p when p < keep_first, else in row
+        keep_first + (p - keep_first) % (rows - keep_first)."""
+        return max_len if self.window is None else max(1, min(max_len, self.keep_first + self.window))
+
+
+@dataclasses.dataclass
+class DeltaRuleConfig:
+    """Gated delta-rule mixer: a per-head matrix state S [qk_dim, v_dim] (fp32), updated per token by
+    S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q,  with a scalar decay g in (0, 1) and a write strength beta in
+    (0, 1) per head and token.  q / k have `n_kv_heads` heads (head h reads q / k head h // (n_heads / n_kv_heads)), pass a causal
+    depthwise convolution of `conv_taps` taps and SiLU (so does v), and are scaled to unit length; o is RMS-normalised per head
+    and gated by SiLU of a projection.  A sequence's decode state is S plus the last conv_taps - 1 projection outputs."""
+    n_heads: int
+    n_kv_heads: int
+    qk_dim: int
+    v_dim: int
+    conv_taps: int
+    unit_eps: float = 1e-6         # q, k <- x / sqrt(sum(x^2) + unit_eps)
+
+    def __post_init__(self):
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if self.conv_taps < 1:
+            raise ValueError("conv_taps >= 1 expected (1 = the current token only)")
+
+    @property
+    def conv_channels(self) -> int:
+        return 2 * self.n_kv_heads * self.qk_dim + self.n_heads * self.v_dim
+
+
+@dataclasses.dataclass
+class LoopConfig:
+    """Blocks start .. stop - 1 (0-based) run `times` times in a row with the same weights, every pass with a cache / state of its
+    own.  With `inject`, each pass first mixes the embedding output x0 back in: x <- W_in [x; x0], W_in [hidden, 2 hidden]."""
+    start: int
+    stop: int
+    times: int
+    inject: bool = True
+
+
+@dataclasses.dataclass
 class BlockMLPConfig:
     """Feed-forward of one block of a heterogeneous stack.  kind `clamped_glu`: y = g * sigmoid(alpha g) * (u + 1) with
     g = min(gate, limit), u = clamp(up, -limit, limit); kind `moe`: `moe.num_experts` SiLU-gated experts of width `ff`, the
-    `moe.top_k` largest router logits (with a router bias) are chosen and weighted by the softmax over the chosen logits."""
-    kind: str                      # clamped_glu | moe
+    `moe.top_k` largest router logits (with a router bias) are chosen and weighted by the softmax over the chosen logits;
+    kind `relu2`: down(relu(up(x))^2), no gate."""
+    kind: str                      # clamped_glu | moe | relu2
     ff: int
     limit: float = 0.0
     alpha: float = 1.702
@@ -89,13 +165,24 @@ class BlockMLPConfig:
 @dataclasses.dataclass
 class BlockConfig:
     """One entry of `ReaLModelConfig.blocks` (a stack whose blocks differ from each other)."""
-    mixer: str                     # latent_attention
+    mixer: str                     # latent_attention | window_attention | delta
     attn: Optional[LatentAttentionConfig] = None
     mlp: Optional[BlockMLPConfig] = None   # None: the block has no feed-forward sublayer
+    wattn: Optional[WindowAttentionConfig] = None
+    delta: Optional[DeltaRuleConfig] = None
 
     def __post_init__(self):
         if isinstance(self.attn, dict):
             self.attn = LatentAttentionConfig(**self.attn)
+        if isinstance(self.wattn, dict):
+            self.wattn = WindowAttentionConfig(**self.wattn)
+        if isinstance(self.delta, dict):
+            self.delta = DeltaRuleConfig(**self.delta)
+        want = {"latent_attention": self.attn, "window_attention": self.wattn, "delta": self.delta}
+        if self.mixer not in want:
+            raise ValueError(f"unknown mixer `{self.mixer}`")
+        if want[self.mixer] is None:
+            raise ValueError(f"a `{self.mixer}` block needs its mixer config")
         if isinstance(self.mlp, dict):
             self.mlp = BlockMLPConfig(**self.mlp)
         if self.mlp is not None and isinstance(self.mlp.moe, dict):
@@ -145,8 +232,29 @@ class ReaLModelConfig:
                                          # the last conv_taps - 1 inputs are part of a sequence's decode state
     logit_softcap: Optional[float] = None  # logits <- cap * tanh(logits / cap)
     fp32_residual: bool = False          # the residual stream is kept in fp32 whatever the compute dtype
+    sinusoidal_positions: bool = False   # x <- embed + pe(p), pe[2i] = sin(p base^(-2i/H)), pe[2i+1] = cos(same), angles in fp32
+    sinusoid_base: float = 10000.0
+    logit_scale: Optional[float] = None  # logits <- logits * logit_scale (fp32)
+    loop: Optional[LoopConfig] = None    # a range of blocks that runs several times (heterogeneous stacks only)
+
+    def layer_runs(self) -> List[Tuple[int, bool]]:
+        """(1-based block index, the run starts a pass of the loop) for every block run, in execution order."""
+        L, lp = self.n_layers, self.loop
+        if lp is None:
+            return [(i, False) for i in range(1, L + 1)]
+        runs = [(i + 1, False) for i in range(lp.start)]
+        for _ in range(lp.times):
+            runs += [(i + 1, i == lp.start) for i in range(lp.start, lp.stop)]
+        return runs + [(i + 1, False) for i in range(lp.stop, L)]
 
     def __post_init__(self):
+        if isinstance(self.loop, dict):
+            self.loop = LoopConfig(**self.loop)
+        if self.loop is not None:
+            if self.blocks is None:
+                raise ValueError("`loop` needs a heterogeneous stack (`blocks`)")
+            if not (0 <= self.loop.start < self.loop.stop <= self.n_layers and self.loop.times >= 1):
+                raise ValueError("loop: 0 <= start < stop <= n_layers and times >= 1 expected")
         if self.is_critic and self.tied_embedding:
             raise ValueError("a critic cannot tie its embedding and output weights")
         if self.blocks is not None:
@@ -155,7 +263,7 @@ class ReaLModelConfig:
                 raise ValueError("`blocks` must describe every layer")
             for i, b in enumerate(self.blocks):
                 if b.mixer != "latent_attention":
-                    raise ValueError(f"block {i}: unknown mixer `{b.mixer}`")
+                    continue
                 src = b.attn.kv_from
                 if src is not None and not (0 <= src < i and self.blocks[src].attn.kv_from is None
                                             and self.blocks[src].attn.kv_rank == b.attn.kv_rank):
@@ -171,12 +279,23 @@ class ReaLModelConfig:
         if self.blocks is not None:
             n = 2 * v * h + h
             for b in self.blocks:
-                a = b.attn
-                n += h * a.n_heads * a.qk_dim + (h * a.kv_rank + a.kv_rank if a.kv_from is None else 0)
-                n += a.kv_rank * a.n_heads * (a.qk_dim + a.v_dim) + a.n_heads * a.v_dim * h + (2 + self.conv_taps) * h
+                if b.mixer == "window_attention":
+                    a = b.wattn
+                    n += h * (a.n_heads * a.qk_dim + a.n_kv_heads * (a.qk_dim + a.v_dim) + a.n_heads) + a.n_heads * a.v_dim * h + h
+                elif b.mixer == "delta":
+                    a = b.delta
+                    n += h * (2 * a.n_kv_heads * a.qk_dim + 2 * a.n_heads * a.v_dim + 2 * a.n_heads) + a.n_heads * a.v_dim * h + h
+                    n += a.conv_channels * a.conv_taps
+                else:
+                    a = b.attn
+                    n += h * a.n_heads * a.qk_dim + (h * a.kv_rank + a.kv_rank if a.kv_from is None else 0)
+                    n += a.kv_rank * a.n_heads * (a.qk_dim + a.v_dim) + a.n_heads * a.v_dim * h + (2 + self.conv_taps) * h
                 if b.mlp is not None:
                     e = b.mlp.moe.num_experts if b.mlp.kind == "moe" else 1
-                    n += e * 3 * h * b.mlp.ff + (e * (h + 1) if b.mlp.kind == "moe" else 0) + (2 + self.conv_taps) * h
+                    mats = 2 if b.mlp.kind == "relu2" else 3
+                    n += e * mats * h * b.mlp.ff + (e * (h + 1) if b.mlp.kind == "moe" else 0) + (2 + self.conv_taps) * h
+            if self.loop is not None and self.loop.inject:
+                n += 2 * h * h
             return n
         qkv = h * self.head_dim * (self.n_q_heads + 2 * self.n_kv_heads)
         attn = qkv + self.n_q_heads * self.head_dim * h

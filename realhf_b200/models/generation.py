@@ -118,14 +118,32 @@ class DecodeState:
             from realhf_b200.models import hetero_block as HB
             first = model.layers[0] if model.layers[0] >= 1 else 1
             self.k, self.v = [], []
-            for i in (j for j in model.layers if 1 <= j <= c.n_layers):
-                a = c.blocks[i - 1].attn
+            # tensors a slot's allocation zeroes / a decode step changes beyond an idempotent append: (tensor, slot dim)
+            self.zeroed: List[Tuple[torch.Tensor, int]] = []
+            run_of_block = {}
+            for r, (i, _) in enumerate(model.local_runs()):
+                b = c.blocks[i - 1]
+                if b.mixer == "window_attention":
+                    w = b.wattn
+                    rows = w.cache_rows(S)
+                    self.k.append(torch.zeros(B, w.n_kv_heads, rows, w.qk_dim, dtype=dt, device=dev))
+                    self.v.append(torch.zeros(B, w.n_kv_heads, rows, w.v_dim, dtype=dt, device=dev))
+                    continue
+                if b.mixer == "delta":
+                    d = b.delta
+                    self.k.append(torch.zeros(B, d.n_heads, d.qk_dim, d.v_dim, dtype=torch.float32, device=dev))
+                    self.v.append(torch.zeros(B, d.conv_taps - 1, d.conv_channels, dtype=torch.float32, device=dev))
+                    self.zeroed += [(self.k[-1], 0), (self.v[-1], 0)]
+                    continue
+                a = b.attn
+                run_of_block[i - 1] = r
                 if a.kv_from is None:
                     self.k.append(torch.zeros(B, HB.ring_rows(c, i - 1, S), a.kv_rank, dtype=dt, device=dev))
                 else:
                     assert a.kv_from + 1 >= first, "a block and the block whose latent it reads must share a pipeline stage"
-                    self.k.append(self.k[a.kv_from + 1 - first])
+                    self.k.append(self.k[run_of_block[a.kv_from]])
                 self.v.append(torch.zeros(2, B, max(c.conv_taps - 1, 0), c.hidden_dim, dtype=torch.float32, device=dev))
+                self.zeroed.append((self.v[-1], 1))
         else:
             # [B, nkv, S, hd] storage viewed as logical [B, S, nkv, hd]
             self.k = [torch.zeros(B, nkv, S, c.head_dim, dtype=dt, device=dev).permute(0, 2, 1, 3) for _ in range(nb)]
@@ -156,10 +174,18 @@ class DecodeState:
         idx = torch.tensor(got, dtype=torch.long, device=self.cache_lens.device)
         self.cache_lens[idx] = 0
         if self.hetero:
-            for v in self.v:
-                if v.shape[2]:
-                    v[:, idx] = 0
+            for t, dim in self.zeroed:
+                if t.numel():
+                    t.index_fill_(dim, idx, 0)
         return got
+
+    def slot_dim(self, t: torch.Tensor) -> int:
+        """Which dim of a state tensor enumerates the slots."""
+        if self.hetero:
+            for z, dim in self.zeroed:
+                if z is t:
+                    return dim
+        return 0
 
     def release(self, slots: List[int]):
         for s_ in slots:
@@ -198,6 +224,8 @@ def _final_logits(model: ReaLModel, hidden: torch.Tensor) -> torch.Tensor:
     lg = OF.linear(hidden, model.head_weight())
     if model.ctx.tp_size > 1:
         lg = TP._gather_last_dim(lg, model.ctx)
+    if model.config.logit_scale is not None:
+        lg = lg.float() * model.config.logit_scale
     if model.config.logit_softcap is not None:
         lg = OF.softcap_logits(lg, model.config.logit_softcap)
     return lg
@@ -251,10 +279,7 @@ class StepSession:
             if id(a) in done:
                 continue
             done.add(id(a))
-            if a.dim() == 4:          # [2, B, taps - 1, H]
-                b_[:, : old.B] = a
-            else:
-                b_[: old.B] = a
+            b_.narrow(old.slot_dim(a), 0, old.B).copy_(a)
         new.free_slots = old.free_slots + list(range(old.B, B))
         self.state = new
 
@@ -371,8 +396,9 @@ def generate(model: ReaLModel, input_ids: torch.Tensor, cu_seqlens: torch.Tensor
     if use_graph and state.graph is None:
         state.input_ids.copy_(nxt)
         lens_backup = state.cache_lens.clone()
-        # a heterogeneous stack's step also shifts the convolution state (the cache append at `cache_lens` is idempotent)
-        conv_backup = [v.clone() for v in state.v] if state.hetero else None
+        # a heterogeneous stack's step also shifts convolution states and updates recurrent states (the cache append at
+        # `cache_lens` is idempotent)
+        conv_backup = [t.clone() for t, _ in state.zeroed] if state.hetero else None
         s = torch.cuda.Stream(dev)
         s.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(s):
@@ -380,8 +406,8 @@ def generate(model: ReaLModel, input_ids: torch.Tensor, cu_seqlens: torch.Tensor
         torch.cuda.current_stream(dev).wait_stream(s)
         state.cache_lens.copy_(lens_backup)
         if conv_backup is not None:
-            for v, b_ in zip(state.v, conv_backup):
-                v.copy_(b_)
+            for (t, _), b_ in zip(state.zeroed, conv_backup):
+                t.copy_(b_)
         graph = torch.cuda.CUDAGraph()
         launches.begin_capture()
         with torch.cuda.graph(graph):

@@ -1,15 +1,20 @@
 """Blocks of a heterogeneous stack (`ReaLModelConfig.blocks`): packed (prefill / inference) and one-token (decode) forms.
 
 A block is  x <- x + post_norm(mixer(conv(norm(x))));  x <- x + post_norm(ff(conv(norm(x))))  on a residual stream that stays
-fp32 when `fp32_residual` is set.  `ReaLModel.forward` / `ReaLModel.decode_step` own the layer loop and the embedding / head;
-`models.generation.DecodeState` owns the per-sequence state the blocks read and write:
+fp32 when `fp32_residual` is set (post_norm and conv are optional: `sandwich_norm`, `conv_taps`).  `ReaLModel.forward` /
+`ReaLModel.decode_step` own the loop over block RUNS (`ReaLModelConfig.layer_runs`: a block inside `config.loop` runs several times,
+each run with its own state), the embedding and the head; `models.generation.DecodeState` owns the per-sequence state, two tensors
+per run (`state.k[r]`, `state.v[r]`), by mixer:
 
-  * latent cache of block i (`state.k[li]`, [n_slots, R, kv_rank], model dtype): a ring, position p in row p % R.  A block
-    with `kv_from = j` holds no cache of its own: its entry is the SAME tensor as block j's.
-  * convolution state of block i (`state.v[li]`, [2, n_slots, taps - 1, hidden] fp32): the normalised inputs of the last
-    taps - 1 tokens, for the mixer ([0]) and the feed-forward ([1]).
+  * latent attention: `k[r]` the latent ring [n_slots, R, kv_rank] (model dtype; position p in row p % R; a block with
+    `kv_from = j` holds the SAME tensor as block j), `v[r]` the convolution state [2, n_slots, taps - 1, hidden] fp32 (the normalised
+    inputs of the last taps - 1 tokens of the mixer [0] and the feed-forward [1]);
+  * window attention: `k[r]` keys [n_slots, G, rows, d], `v[r]` normalised values [n_slots, G, rows, dv] (model dtype); position p
+    in row p below `keep_first`, else in a ring of the remaining rows (`WindowAttentionConfig.cache_rows`);
+  * delta rule: `k[r]` the matrix states [n_slots, H, d, dv] fp32, `v[r]` the last taps - 1 projection outputs
+    [n_slots, taps - 1, C] fp32.
 
-Inference only (no autograd through these kernels) and not tensor-parallel.
+Inference only (no autograd through these kernels) and not tensor-parallel.  A stack with a loop runs on one pipeline stage.
 """
 
 from __future__ import annotations
@@ -21,6 +26,7 @@ import torch
 
 from realhf_b200.ops import attention as attn_ops
 from realhf_b200.ops import functional as OF
+from realhf_b200.ops import recurrent as rec_ops
 
 
 @dataclasses.dataclass
@@ -34,6 +40,7 @@ class PackedMeta:
     latents: Dict[int, torch.Tensor] = dataclasses.field(default_factory=dict)   # block index (0-based) -> packed latent [T, rank]
     cu_seqlens: Optional[torch.Tensor] = None
     max_seqlen: Optional[int] = None
+    seq_slot: Optional[torch.Tensor] = None   # [n_seqs] int32 state slot of every sequence (None: keep no state)
 
 
 def packed_meta(cu_seqlens: torch.Tensor, total: int, slots: Optional[torch.Tensor] = None, state=None,
@@ -48,7 +55,8 @@ def packed_meta(cu_seqlens: torch.Tensor, total: int, slots: Optional[torch.Tens
     else:
         tok_slot = slots.to(dev).int()[seq].contiguous()
     return PackedMeta(pos, remain, tok_slot, state.k if state is not None else None, state.v if state is not None else None,
-                      cu_seqlens=cu_seqlens.int().contiguous(), max_seqlen=max_seqlen)
+                      cu_seqlens=cu_seqlens.int().contiguous(), max_seqlen=max_seqlen,
+                      seq_slot=slots.to(dev).int().contiguous() if slots is not None else None)
 
 
 def _mlp(model, i: int, h: torch.Tensor, mcfg) -> torch.Tensor:
@@ -56,17 +64,81 @@ def _mlp(model, i: int, h: torch.Tensor, mcfg) -> torch.Tensor:
     if mcfg.kind == "moe":
         from realhf_b200.models import moe
         return moe.moe_forward(model, i, h, mcfg.moe)
+    if mcfg.kind == "relu2":
+        return OF.linear(OF.relu2_linear(h, p[f"{i}.mlp.up.weight"]), p[f"{i}.mlp.down.weight"])
     a = OF.clamped_gated_linear(h, p[f"{i}.mlp.gate_up.weight"], mcfg.limit, mcfg.alpha)
     return OF.linear(a, p[f"{i}.mlp.down.weight"])
 
 
+def _window_attention_packed(model, i: int, li: int, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+    c, p = model.config, model.p
+    a = c.blocks[i - 1].wattn
+    keep = meta.k is not None
+    qkvg = OF.linear(h, p[f"{i}.attn.qkvg.weight"], p.get(f"{i}.attn.qkvg.bias"))
+    v_n = attn_ops.value_norm_store(qkvg, a, c.layer_norm_epsilon, meta.k[li] if keep else None, meta.v[li] if keep else None,
+                                    meta.tok_slot, meta.pos, meta.remain)
+    o = attn_ops.sink_window_attention(qkvg, v_n, a, p.get(f"{i}.attn.temp.weight"), p.get(f"{i}.attn.sink.weight"), meta.pos,
+                                       meta.cu_seqlens, meta.max_seqlen)
+    return OF.linear(o, p[f"{i}.attn.o.weight"])
+
+
+def _window_attention_decode(model, i: int, li: int, h: torch.Tensor, k_caches, v_caches, cache_lens, slots) -> torch.Tensor:
+    c, p = model.config, model.p
+    a = c.blocks[i - 1].wattn
+    qkvg = OF.linear(h, p[f"{i}.attn.qkvg.weight"], p.get(f"{i}.attn.qkvg.bias"))
+    o = attn_ops.sink_window_decode_attention(qkvg, a, p.get(f"{i}.attn.temp.weight"), p.get(f"{i}.attn.sink.weight"), k_caches[li],
+                                              v_caches[li], cache_lens, slots, c.layer_norm_epsilon)
+    return OF.linear(o, p[f"{i}.attn.o.weight"])
+
+
+def _delta_packed(model, i: int, li: int, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+    c, p = model.config, model.p
+    d = c.blocks[i - 1].delta
+    keep = meta.k is not None
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    u = rec_ops.delta_prepare(proj, p[f"{i}.attn.conv.weight"], p[f"{i}.attn.A_log.weight"], p[f"{i}.attn.dt_bias.weight"], d, meta.pos,
+                              meta.v[li] if keep else None, meta.tok_slot, meta.remain)
+    o = rec_ops.delta_rule_scan(u, d, meta.cu_seqlens, meta.k[li] if keep else None, meta.seq_slot if keep else None)
+    return OF.linear(_delta_out(model, i, d, o, proj), p[f"{i}.attn.o.weight"])
+
+
+def _delta_out(model, i: int, d, o: torch.Tensor, proj: torch.Tensor) -> torch.Tensor:
+    g0 = 2 * d.n_kv_heads * d.qk_dim + d.n_heads * d.v_dim
+    return rec_ops.gated_head_norm(o, model.p[f"{i}.attn.o_norm.weight"], proj[:, g0:g0 + d.n_heads * d.v_dim],
+                                   model.config.layer_norm_epsilon, model.dtype)
+
+
+def _delta_decode(model, i: int, li: int, h: torch.Tensor, k_caches, v_caches, slots) -> torch.Tensor:
+    c, p = model.config, model.p
+    d = c.blocks[i - 1].delta
+    proj = OF.linear(h, p[f"{i}.attn.in.weight"])
+    u = rec_ops.delta_prepare_step(proj, p[f"{i}.attn.conv.weight"], p[f"{i}.attn.A_log.weight"], p[f"{i}.attn.dt_bias.weight"], d,
+                                   v_caches[li], slots)
+    o = rec_ops.delta_rule_step(u, d, k_caches[li], slots)
+    return OF.linear(_delta_out(model, i, d, o, proj), p[f"{i}.attn.o.weight"])
+
+
+def loop_inject(model, i: int, x: torch.Tensor, x0: torch.Tensor) -> torch.Tensor:
+    """Start of a pass of the loop: x <- W_in [x; x0] (x0 = the embedding output), back on the residual stream's dtype."""
+    y = OF.linear(OF.concat_cast(x, x0, model.dtype), model.p[f"{i}.loop_in.weight"])
+    return y.to(x.dtype)
+
+
 def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
-    """Block i (1-based layer index; li = index among this stage's blocks) on the packed batch; x [T, H] is updated in place."""
+    """Block i (1-based layer index; li = index among this stage's block runs) on the packed batch; x [T, H] is updated in place."""
     c, p = model.config, model.p
     b = c.blocks[i - 1]
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
     keep = meta.k is not None
+    if b.mixer != "latent_attention":
+        h = OF.sublayer_input(x, p[f"{i}.attn.ln.weight"], G, eps, None, None, model.dtype)
+        y = _window_attention_packed(model, i, li, h, meta) if b.mixer == "window_attention" else _delta_packed(model, i, li, h, meta)
+        OF.residual_add_norm_(x, y, p.get(f"{i}.attn.ln_post.weight"), G, eps)
+        if b.mlp is not None:
+            h = OF.sublayer_input(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, model.dtype)
+            OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
+        return x
     conv = meta.v[li] if keep and c.conv_taps else None
     h = OF.sublayer_input(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"), meta.pos, model.dtype,
                           conv[0] if conv is not None else None, meta.tok_slot, meta.remain)
@@ -96,6 +168,17 @@ def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.T
     b = c.blocks[i - 1]
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
+    if b.mixer != "latent_attention":
+        h = OF.sublayer_input_step(x, p[f"{i}.attn.ln.weight"], G, eps, None, None, slots, model.dtype)
+        if b.mixer == "window_attention":
+            y = _window_attention_decode(model, i, li, h, k_caches, v_caches, cache_lens, slots)
+        else:
+            y = _delta_decode(model, i, li, h, k_caches, v_caches, slots)
+        OF.residual_add_norm_(x, y, p.get(f"{i}.attn.ln_post.weight"), G, eps)
+        if b.mlp is not None:
+            h = OF.sublayer_input_step(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, slots, model.dtype)
+            OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
+        return x
     conv = v_caches[li] if c.conv_taps else None
     h = OF.sublayer_input_step(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"),
                                conv[0] if conv is not None else None, slots, model.dtype)
@@ -121,6 +204,8 @@ def ring_rows(cfg, block: int, max_len: int) -> int:
     that read it, or max_len when one of them sees the whole prefix."""
     need = 0
     for j, b in enumerate(cfg.blocks):
+        if b.mixer != "latent_attention":
+            continue
         if j == block or b.attn.kv_from == block:
             if b.attn.window is None:
                 return max_len

@@ -78,6 +78,7 @@ class ModelOutput:
     is_critic: bool = False
     _logits: Optional[torch.Tensor] = None
     softcap: Optional[float] = None      # models with a soft cap on the logits: `logits` are the capped fp32 values
+    logit_scale: Optional[float] = None  # models with a fixed factor on the logits: `logits` are the scaled fp32 values
 
     @property
     def logits(self) -> torch.Tensor:
@@ -88,6 +89,8 @@ class ModelOutput:
                 tp = self.ctx is not None and self.ctx.tp_size > 1
                 lg = OF.linear(TP.copy_to_tp(self.hidden, self.ctx) if tp else self.hidden, self.head_weight)
                 self._logits = TP.gather_last_dim(lg, self.ctx) if tp else lg
+                if self.logit_scale is not None:
+                    self._logits = self._logits.float() * self.logit_scale
                 if self.softcap is not None:
                     self._logits = OF.softcap_logits(self._logits, self.softcap)
         return self._logits
@@ -102,8 +105,13 @@ class ModelOutput:
         """fp32 log p(labels[i] | hidden[rows[i]]) (rows defaults to all tokens)."""
         h = self.hidden if rows is None else self.hidden.index_select(0, rows)
         if self.softcap is not None:  # the fused LM-head + log-prob kernel has no cap stage: capped logits are materialised
-            lg = OF.softcap_logits(OF.linear(h, self.head_weight), self.softcap)
+            lg = OF.linear(h, self.head_weight)
+            if self.logit_scale is not None:
+                lg = lg.float() * self.logit_scale
+            lg = OF.softcap_logits(lg, self.softcap)
             return OF.logprob_from_logits(lg, labels, mask_bits, 1.0 / temperature)[0]
+        if self.logit_scale is not None:  # a fixed factor on the logits is a factor on the inverse temperature
+            temperature = temperature / self.logit_scale
         if self.ctx is not None and self.ctx.tp_size > 1:
             local = OF.linear(TP.copy_to_tp(h, self.ctx), self.head_weight)  # column-parallel head: d(hidden) is summed over TP
             return TP.vocab_parallel_logprobs(local, labels, self.ctx, temperature, mask_bits)
@@ -122,6 +130,8 @@ class ReaLModel(nn.Module):
         self.ctx = ctx if ctx is not None else ParallelContext.single()
         if config.blocks is not None and self.ctx.tp_size > 1:
             raise NotImplementedError("heterogeneous stacks (`config.blocks`) are not tensor-parallel")
+        if config.loop is not None and self.ctx.pp_size > 1:
+            raise NotImplementedError("a stack with a loop (`config.loop`) runs on one pipeline stage")
         self.dtype = dtype
         self.device = torch.device(device)
         if layer_range is None:
@@ -343,8 +353,11 @@ class ReaLModel(nn.Module):
         return s
 
     # ------------------------------------------------------------------ layers
-    def _embed(self, input_ids, position_ids):
+    def _embed(self, input_ids, position_ids, slots=None):
         c = self.config
+        if c.sinusoidal_positions:  # (position-free otherwise) fp32 gather + sin / cos in one pass; not vocabulary-parallel
+            assert self.ctx.tp_size == 1
+            return OF.embed_sinusoid(input_ids, self.p["0.wte.weight"], position_ids, c.sinusoid_base, slots)
         x = TP.vocab_parallel_embedding(input_ids, self.p["0.wte.weight"], self.ctx, sp=self.sequence_parallel)
         if not c.apply_rotary and c.n_positions:
             pe = F.embedding(position_ids.long() + c.abs_position_embedding_offset, self.p["0.wpe.weight"])
@@ -584,8 +597,9 @@ class ReaLModel(nn.Module):
             x = TP.gather_from_sp(x, self.ctx, reduce_scatter_bwd=False)
         return ModelOutput(hidden=x, head_weight=self.head_weight(), ctx=self.ctx, is_critic=c.is_critic)
 
-    def _forward_hetero(self, input_ids, cu_seqlens, hidden, kv_sink, max_seqlen=None):
-        """Packed forward of a heterogeneous stack (inference only: its kernels have no backward)."""
+    def _forward_hetero(self, input_ids, cu_seqlens, hidden, kv_sink, max_seqlen=None, trace: Optional[list] = None):
+        """Packed forward of a heterogeneous stack (inference only: its kernels have no backward).  `trace`: a list that receives a
+        copy of the residual stream after every block run."""
         from realhf_b200.models import hetero_block as HB
         c = self.config
         assert not torch.is_grad_enabled() or not any(p.requires_grad for p in self.p.values()), \
@@ -595,19 +609,29 @@ class ReaLModel(nn.Module):
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         meta = HB.packed_meta(cu_seqlens, T, slots, state, max_seqlen)
-        x, li = hidden, 0
+        x = x0 = hidden
         with torch.no_grad():
-            for i in self.layers:
-                if i == 0:
-                    x = self._embed(input_ids, meta.pos)
-                elif i <= c.n_layers:
-                    x = HB.block_packed(self, i, li, x, meta)
-                    li += 1
-                    if i == c.n_layers:
-                        x = HB.final_norm(self, x)
+            if 0 in self.layers:
+                x = x0 = self._embed(input_ids, meta.pos)
+            for li, (i, starts_pass) in enumerate(self.local_runs()):
+                if starts_pass and c.loop.inject:
+                    x = HB.loop_inject(self, i, x, x0)
+                elif x is x0 and c.loop is not None:
+                    x = x0.clone()  # the blocks update the stream in place; the loop reads the embedding output again
+                x = HB.block_packed(self, i, li, x, meta)
+                if trace is not None:
+                    trace.append(x.clone())
+            if c.n_layers in self.layers:
+                x = HB.final_norm(self, x)
         if not self.is_last_stage:
             return x
-        return ModelOutput(hidden=x, head_weight=self.head_weight(), ctx=self.ctx, is_critic=c.is_critic, softcap=c.logit_softcap)
+        return ModelOutput(hidden=x, head_weight=self.head_weight(), ctx=self.ctx, is_critic=c.is_critic, softcap=c.logit_softcap,
+                           logit_scale=c.logit_scale)
+
+    def local_runs(self) -> List[Tuple[int, bool]]:
+        """The block runs of this stage in execution order: (1-based block index, the run starts a pass of `config.loop`)."""
+        mine = set(self.layers)
+        return [r for r in self.config.layer_runs() if r[0] in mine]
 
     def _n_unckpt_blocks(self, n_tokens: int) -> int:
         """How many transformer blocks of this forward pass may keep their activations instead of being recomputed.
@@ -642,15 +666,17 @@ class ReaLModel(nn.Module):
         c = self.config
         if c.blocks is not None:
             from realhf_b200.models import hetero_block as HB
-            x, li = hidden, 0
-            for i in self.layers:
-                if i == 0:
-                    x = self._embed(input_ids, None)
-                elif i <= c.n_layers:
-                    x = HB.block_decode(self, i, li, x, k_caches, v_caches, cache_lens, slots)
-                    li += 1
-                    if i == c.n_layers:
-                        x = HB.final_norm(self, x)
+            x = x0 = hidden
+            if 0 in self.layers:
+                x = x0 = self._embed(input_ids, cache_lens, slots)   # a new token's position is its slot's length
+            for li, (i, starts_pass) in enumerate(self.local_runs()):
+                if starts_pass and c.loop.inject:
+                    x = HB.loop_inject(self, i, x, x0)
+                elif x is x0 and c.loop is not None:
+                    x = x0.clone()
+                x = HB.block_decode(self, i, li, x, k_caches, v_caches, cache_lens, slots)
+            if c.n_layers in self.layers:
+                x = HB.final_norm(self, x)
             return x
         assert slots is None, "slot indirection is a feature of heterogeneous stacks"
         nq, nkv = self._local_heads()

@@ -94,6 +94,25 @@ def layer_param_specs(cfg: ReaLModelConfig, layer_idx: int, tied_head_copy: bool
     return out
 
 
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def wattn_sections(w) -> Tuple[int, ...]:
+    """Rows of the fused input projection of a window-attention block: [queries | keys | values | output-gate logits].  The gate
+    section (one row per head) is padded to a multiple of 8 rows so that the fused tensor keeps 16-byte row groups; the padding
+    rows are never read."""
+    sec = (w.n_heads * w.qk_dim, w.n_kv_heads * w.qk_dim, w.n_kv_heads * w.v_dim)
+    return sec + ((_pad8(w.n_heads),) if w.out_gate else ())
+
+
+def delta_sections(d) -> Tuple[int, ...]:
+    """Rows of the fused input projection of a delta-rule block: [q | k | v | output gate | write strength, decay input].  The
+    convolution acts on the first three sections, which are therefore contiguous; the last section holds one row per head for
+    beta, then one per head for the decay, padded to a multiple of 8."""
+    return (d.n_kv_heads * d.qk_dim, d.n_kv_heads * d.qk_dim, d.n_heads * d.v_dim, d.n_heads * d.v_dim, _pad8(2 * d.n_heads))
+
+
 def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSpec]:
     """Specs of block `layer_idx` of a heterogeneous stack (`cfg.blocks`).  Projections that read the same input are one tensor
     made of sections: `attn.q_dkv` = [queries | latent down-projection] (the second section is absent in a block that reads
@@ -106,17 +125,40 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
 
     def add(*args, **kw):
         out.append(P(*args, **kw))
+    if cfg.loop is not None and cfg.loop.inject and layer_idx == cfg.loop.start + 1:
+        add("loop_in.weight", (H, 2 * H), None)
     add("attn.ln.weight", (H,), None, init="ones")
     if cfg.conv_taps:
         add("attn.canon.weight", (H, cfg.conv_taps), None)
-    own = a.kv_from is None
-    q_sec = (a.n_heads * a.qk_dim,) + ((a.kv_rank,) if own else ())
-    add("attn.q_dkv.weight", (sum(q_sec), H), None, q_sec)
-    if own:
-        add("attn.dkv_ln.weight", (a.kv_rank,), None, init="ones")
-    kv_sec = (a.n_heads * a.qk_dim, a.n_heads * a.v_dim)
-    add("attn.ukv.weight", (sum(kv_sec), a.kv_rank), None, kv_sec)
-    add("attn.o.weight", (H, a.n_heads * a.v_dim), None)
+    if b.mixer == "window_attention":
+        w = b.wattn
+        sec = wattn_sections(w)
+        add("attn.qkvg.weight", (sum(sec), H), None, sec)
+        if w.qkv_bias:
+            add("attn.qkvg.bias", (sum(sec),), None, sec, init="zeros")
+        if w.head_temp:
+            add("attn.temp.weight", (w.n_heads,), None, init="ones")
+        if w.sink:
+            add("attn.sink.weight", (w.n_heads,), None, init="zeros")
+        add("attn.o.weight", (H, w.n_heads * w.v_dim), None)
+    elif b.mixer == "delta":
+        d = b.delta
+        sec = delta_sections(d)
+        add("attn.in.weight", (sum(sec), H), None, sec)
+        add("attn.conv.weight", (d.conv_channels, d.conv_taps), None)
+        add("attn.A_log.weight", (d.n_heads,), None, init="zeros")
+        add("attn.dt_bias.weight", (d.n_heads,), None, init="zeros")
+        add("attn.o_norm.weight", (d.v_dim,), None, init="ones")
+        add("attn.o.weight", (H, d.n_heads * d.v_dim), None)
+    else:
+        own = a.kv_from is None
+        q_sec = (a.n_heads * a.qk_dim,) + ((a.kv_rank,) if own else ())
+        add("attn.q_dkv.weight", (sum(q_sec), H), None, q_sec)
+        if own:
+            add("attn.dkv_ln.weight", (a.kv_rank,), None, init="ones")
+        kv_sec = (a.n_heads * a.qk_dim, a.n_heads * a.v_dim)
+        add("attn.ukv.weight", (sum(kv_sec), a.kv_rank), None, kv_sec)
+        add("attn.o.weight", (H, a.n_heads * a.v_dim), None)
     if cfg.sandwich_norm:
         add("attn.ln_post.weight", (H,), None, init="ones")
     if b.mlp is not None:
@@ -130,6 +172,9 @@ def _hetero_block_specs(cfg: ReaLModelConfig, layer_idx: int, P) -> List[ParamSp
             add("mlp.router.bias", (E,), None, init="zeros")
             add("mlp.experts.gate_up.weight", (E, 2 * F, H), None)
             add("mlp.experts.down.weight", (E, H, F), None)
+        elif b.mlp.kind == "relu2":
+            add("mlp.up.weight", (F, H), None)
+            add("mlp.down.weight", (H, F), None)
         else:
             add("mlp.gate_up.weight", (2 * F, H), None, (F, F))
             add("mlp.down.weight", (H, F), None)

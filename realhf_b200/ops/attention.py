@@ -321,3 +321,173 @@ def latent_decode_attention(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads: 
         o = lib().latent_decode_core(qa, cache, cache_lens, slots, window if window is not None else 0, splits)
         return torch.bmm(o, wv).transpose(0, 1).reshape(B, n_heads * vd).to(qc.dtype)
     return latent_decode_attention_ref(qc, w_ln, w_ukv, cache, cache_lens, slots, n_heads, qk, vd, scale, window, eps)
+
+
+# ------------------------------------------------------------------------------------------------ window attention with a sink
+# (`WindowAttentionConfig`): grouped key / value heads, no rotation; per-head temperature, linear distance penalty, sliding window
+# that keeps the first tokens, sink logit in the denominator, sigmoid output gate.  Scores, weights and the value norm are fp32.
+# The projection output `qkvg` [T, ld] holds [q (H x d) | k (G x d) | v (G x dv) | gate logits (H, padded)] per row.
+# Caches: k_cache [n_slots, G, rows, d], v_cache [n_slots, G, rows, dv]; position p of a sequence lives in row p when
+# p < keep_first, else in row keep_first + (p - keep_first) % (rows - keep_first).
+
+
+def cache_row(pos, keep_first: int, rows: int):
+    ring = max(rows - keep_first, 1)
+    if isinstance(pos, torch.Tensor):
+        return torch.where(pos < keep_first, pos, keep_first + (pos - keep_first) % ring)
+    return pos if pos < keep_first else keep_first + (pos - keep_first) % ring
+
+
+def head_slopes(n_heads: int, slope_base: Optional[float], device) -> torch.Tensor:
+    """fp32 [n_heads]: 2^(-slope_base (h + 1) / n_heads), zeros without a distance term."""
+    if slope_base is None:
+        return torch.zeros(n_heads, dtype=torch.float32, device=device)
+    return torch.exp2(-slope_base * torch.arange(1, n_heads + 1, dtype=torch.float32, device=device) / n_heads)
+
+
+def _wa_offsets(a):
+    nq, nk, nv = a.n_heads * a.qk_dim, a.n_kv_heads * a.qk_dim, a.n_kv_heads * a.v_dim
+    return nq, nq + nk, nq + nk + nv
+
+
+def value_norm_store_ref(qkvg, a, eps, k_cache, v_cache, tok_slot, pos, remain):
+    T = qkvg.shape[0]
+    oq, ok_, ov = _wa_offsets(a)
+    v = qkvg[:, ok_:ov].float().view(T, a.n_kv_heads, a.v_dim)
+    if a.value_norm:
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    v = v.to(qkvg.dtype)
+    if k_cache is not None:
+        rows = k_cache.shape[2]
+        ring = rows - a.keep_first
+        keep = (tok_slot >= 0) & ((pos < a.keep_first) | (remain < ring))
+        r = cache_row(pos.long(), a.keep_first, rows)[keep]
+        s = tok_slot[keep].long()
+        k_cache[s, :, r] = qkvg[keep, oq:ok_].view(-1, a.n_kv_heads, a.qk_dim)
+        v_cache[s, :, r] = v[keep]
+    return v.reshape(T, a.n_kv_heads * a.v_dim)
+
+
+def value_norm_store(qkvg, a, eps: float, k_cache, v_cache, tok_slot, pos, remain):
+    """Packed prefill: the value heads of `qkvg`, each divided by its root mean square (fp32; `a.value_norm`), as [T, G * dv] in
+    the model dtype; with caches, also writes every token's key and normalised value that a later decode step can still see
+    (the first `keep_first` positions and the last `rows - keep_first` of each sequence) into its slot."""
+    if use_native(qkvg):
+        T = qkvg.shape[0]
+        out = torch.empty(T, a.n_kv_heads * a.v_dim, dtype=qkvg.dtype, device=qkvg.device)
+        lib().value_norm_store(qkvg, out, k_cache, v_cache, tok_slot if k_cache is not None else None, pos,
+                               remain if k_cache is not None else None, a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim, a.keep_first,
+                               bool(a.value_norm), eps)
+        return out
+    return value_norm_store_ref(qkvg, a, eps, k_cache, v_cache, tok_slot, pos, remain)
+
+
+def _sink_softmax_pv(s, ok, sink_h, v):
+    """fp32 scores s [Lq, Lk], visibility ok, sink logit (tensor scalar or None) -> softmax-with-sink weights @ v."""
+    s = s.masked_fill(~ok, float("-inf"))
+    mx = s.max(-1, keepdim=True).values
+    if sink_h is not None:
+        mx = torch.maximum(mx, sink_h)
+    mx = torch.where(torch.isfinite(mx), mx, torch.zeros_like(mx))
+    e = torch.exp(s - mx)
+    den = e.sum(-1, keepdim=True)
+    if sink_h is not None:
+        den = den + torch.exp(sink_h - mx)
+    return (e / den) @ v
+
+
+def sink_window_attention_ref(qkvg, v_n, a, temp, sink, cu_seqlens):
+    T = qkvg.shape[0]
+    H, G, d, dv = a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim
+    oq, ok_, ov = _wa_offsets(a)
+    q = qkvg[:, :oq].float().view(T, H, d)
+    k = qkvg[:, oq:ok_].float().view(T, G, d)
+    v = v_n.float().view(T, G, dv)
+    gate = torch.sigmoid(qkvg[:, ov:ov + H].float()) if a.out_gate else None
+    slopes = head_slopes(H, a.slope_base, qkvg.device)
+    out = torch.zeros(T, H, dv, dtype=torch.float32, device=qkvg.device)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        s0, e0 = cu[b], cu[b + 1]
+        if e0 == s0:
+            continue
+        L = e0 - s0
+        i = torch.arange(L, device=qkvg.device).unsqueeze(1)
+        j = torch.arange(L, device=qkvg.device).unsqueeze(0)
+        ok = j <= i
+        if a.window is not None:
+            ok = ok & ((i - j < a.window) | (j < a.keep_first))
+        dist = (i - j).float()
+        for h in range(H):
+            g = h // (H // G)
+            sc = (q[s0:e0, h] @ k[s0:e0, g].T) * a.scale
+            if temp is not None:
+                sc = sc * temp[h].float()
+            sc = sc - slopes[h] * dist
+            out[s0:e0, h] = _sink_softmax_pv(sc, ok, sink[h].float() if sink is not None else None, v[s0:e0, g])
+    if gate is not None:
+        out = out * gate.unsqueeze(-1)
+    return out.reshape(T, H * dv).to(qkvg.dtype)
+
+
+def sink_window_attention(qkvg, v_n, a, temp, sink, pos, cu_seqlens, max_seqlen=None):
+    """Packed causal attention of a window-attention block over the batch's own keys (every sequence starts at position 0):
+    softmax_j(q_i . k_j * scale * temp_h - slope_h (i - j)) with the sink logit in the denominator, over j <= i with
+    i - j < window or j < keep_first; head h's output times sigmoid(gate logit h).  Returns [T, H * dv] in the model dtype."""
+    if use_native(qkvg):
+        T = qkvg.shape[0]
+        out = torch.empty(T, a.n_heads * a.v_dim, dtype=qkvg.dtype, device=qkvg.device)
+        lib().sink_window_attention(qkvg, v_n, out, temp, sink, pos, a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim, a.scale,
+                                    a.window if a.window is not None else -1, a.keep_first,
+                                    a.slope_base if a.slope_base is not None else -1.0, bool(a.out_gate))
+        return out
+    return sink_window_attention_ref(qkvg, v_n, a, temp, sink, cu_seqlens)
+
+
+def sink_window_decode_attention_ref(qkvg, a, temp, sink, k_cache, v_cache, cache_lens, slots, eps):
+    B = qkvg.shape[0]
+    H, G, d, dv = a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim
+    oq, ok_, ov = _wa_offsets(a)
+    rows = k_cache.shape[2]
+    slopes = head_slopes(H, a.slope_base, qkvg.device)
+    out = torch.zeros(B, H, dv, dtype=torch.float32, device=qkvg.device)
+    for b in range(B):
+        s = int(slots[b]) if slots is not None else b
+        n = int(cache_lens[s])                                     # the new token's position
+        v_new = qkvg[b, ok_:ov].float().view(G, dv)
+        if a.value_norm:
+            v_new = v_new * torch.rsqrt(v_new.pow(2).mean(-1, keepdim=True) + eps)
+        r = cache_row(n, a.keep_first, rows)
+        k_cache[s, :, r] = qkvg[b, oq:ok_].view(G, d)
+        v_cache[s, :, r] = v_new.to(v_cache.dtype)
+        j = torch.arange(n + 1, device=qkvg.device)
+        if a.window is not None:
+            j = j[(n - j < a.window) | (j < a.keep_first)]
+        rj = cache_row(j, a.keep_first, rows)
+        kk = k_cache[s][:, rj].float()                             # [G, n_keys, d]
+        vv = v_cache[s][:, rj].float()
+        q = qkvg[b, :oq].float().view(H, d)
+        for h in range(H):
+            g = h // (H // G)
+            sc = (kk[g] @ q[h]) * a.scale
+            if temp is not None:
+                sc = sc * temp[h].float()
+            sc = (sc - slopes[h] * (n - j).float()).unsqueeze(0)
+            out[b, h] = _sink_softmax_pv(sc, torch.ones_like(sc, dtype=torch.bool), sink[h].float() if sink is not None else None, vv[g])[0]
+        if a.out_gate:
+            out[b] = out[b] * torch.sigmoid(qkvg[b, ov:ov + H].float()).unsqueeze(-1)
+    return out.reshape(B, H * dv).to(qkvg.dtype)
+
+
+def sink_window_decode_attention(qkvg, a, temp, sink, k_cache, v_cache, cache_lens, slots, eps: float):
+    """One new token per row against the caches of its slot (slots None: row b is slot b).  The row's key and normalised value
+    are appended in place at the row of position cache_lens[slot] (cache_lens itself is not changed), then the token attends to
+    every cached position its window and `keep_first` allow, itself included.  Returns [B, H * dv] in the model dtype."""
+    if use_native(qkvg):
+        B = qkvg.shape[0]
+        out = torch.empty(B, a.n_heads * a.v_dim, dtype=qkvg.dtype, device=qkvg.device)
+        lib().sink_window_decode_attention(qkvg, out, temp, sink, k_cache, v_cache, cache_lens, slots, a.n_heads, a.n_kv_heads, a.qk_dim,
+                                           a.v_dim, a.scale, a.window if a.window is not None else -1, a.keep_first,
+                                           a.slope_base if a.slope_base is not None else -1.0, bool(a.out_gate), bool(a.value_norm), eps)
+        return out
+    return sink_window_decode_attention_ref(qkvg, a, temp, sink, k_cache, v_cache, cache_lens, slots, eps)

@@ -705,3 +705,56 @@ def softcap_logits(logits, cap: Optional[float]):
     if use_native(logits):
         return lib().softcap(logits.contiguous(), cap)
     return cap * torch.tanh(logits.float() / cap)
+
+
+# ------------------------------------------------------------------------------------------------ sinusoidal positions, relu^2
+
+
+def sinusoid_inv_freq(width: int, base: float, device) -> torch.Tensor:
+    """fp32 [width // 2]: base^(-2i / width), rounded once from float64."""
+    i = torch.arange(width // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / width).float().to(device)
+
+
+def embed_sinusoid_ref(ids, wte, pos, inv_freq):
+    ang = pos.float().unsqueeze(1) * inv_freq.unsqueeze(0)            # fp32 product, as the kernel forms it
+    x = F.embedding(ids.long(), wte).float()
+    x[:, 0::2] += torch.sin(ang)
+    x[:, 1::2] += torch.cos(ang)
+    return x
+
+
+def embed_sinusoid(ids, wte, pos, base: float = 10000.0, slots=None):
+    """fp32 x [T, W] = wte[ids] + pe(p): pe[2i] = sin(p f_i), pe[2i + 1] = cos(p f_i), f_i = base^(-2i / W); positions and angles in
+    fp32 with exact sinf / cosf.  p = pos[t], or pos[slots[t]] with `slots` (decode: `pos` is the per-slot length table)."""
+    W = wte.shape[1]
+    inv_freq = cached_on(wte, "_sin_inv_freq", lambda w: (base, sinusoid_inv_freq(W, base, w.device)))
+    if inv_freq[0] != base:
+        inv_freq = (base, sinusoid_inv_freq(W, base, wte.device))
+    if use_native(wte):
+        out = torch.empty(ids.shape[0], W, dtype=torch.float32, device=wte.device)
+        lib().embed_sinusoid(ids, wte, pos, slots, inv_freq[1], out)
+        return out
+    return embed_sinusoid_ref(ids, wte, pos if slots is None else pos[slots.long()], inv_freq[1])
+
+
+def relu2(x):
+    """relu(x)^2, elementwise, in x's dtype (fp32 inside)."""
+    if use_native(x):
+        return lib().relu2(x.contiguous())
+    r = torch.relu(x.float())
+    return (r * r).to(x.dtype)
+
+
+def relu2_linear(x, w_up):
+    """relu(x @ w_up^T)^2."""
+    return relu2(linear(x, w_up))
+
+
+def concat_cast(a, b, out_dtype):
+    """[a | b] along the last dim, in out_dtype (one pass; the input of a projection that reads two streams)."""
+    if use_native(a):
+        out = torch.empty(a.shape[0], a.shape[1] + b.shape[1], dtype=out_dtype, device=a.device)
+        lib().concat_cast(a.contiguous(), b.contiguous(), out)
+        return out
+    return torch.cat([a, b], -1).to(out_dtype)

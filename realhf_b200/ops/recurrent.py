@@ -1,0 +1,173 @@
+"""Recurrent mixers: the gated delta rule (`DeltaRuleConfig`) in packed (prefill) and one-token (decode) form.
+
+Per head, with a matrix state S [d, dv] in fp32:   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+(the output is read after the update, so it contains what this token just wrote).  Everything that enters the recurrence is fp32.
+
+The stages, each = PyTorch reference (CPU tensors, also the numerics oracle of the kernel tests) + sm_100a kernel (`csrc/delta.cu`):
+
+  delta_prepare(_step)   the fused projection output `proj` [T, ld] = [q (G x d) | k (G x d) | v (H x dv) | gate (H x dv) | beta
+                         logits (H) | decay inputs (H) | padding] -> fp32 `u` [T, C + 2H] = [q | k | v | beta | g]:  causal depthwise
+                         convolution + SiLU over the first C = 2 G d + H dv channels (inputs before a sequence's first token are zero; the packed
+                         form leaves the last taps - 1 raw inputs of every sequence in `conv_state` [n_slots, taps - 1, C] fp32,
+                         oldest first; the step form reads and shifts it), q and k scaled to unit length per head (q also by
+                         d^-1/2), beta = sigmoid, g = exp(-exp(A_log) softplus(a + dt_bias)).
+  delta_rule_scan / _step  the recurrence over each sequence from S = 0 (leaving S in `s_state` [n_slots, H, d, dv] fp32), or one
+                         token per row against `s_state`, updated in place.  o [T, H, dv] fp32.
+  gated_head_norm        o / rms(o) * w * silu(gate) per head -> [T, H * dv] in the model dtype.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from realhf_b200.ops import lib, use_native
+
+
+def _offsets(d):
+    nqk, nv, H = d.n_kv_heads * d.qk_dim, d.n_heads * d.v_dim, d.n_heads
+    C = 2 * nqk + nv
+    return nqk, nv, H, C
+
+
+def _finish_prepare(y, proj, d, A_log, dt_bias):
+    """y [T, C] fp32 = convolved channels -> u [T, C + 2H]."""
+    nqk, nv, H, C = _offsets(d)
+    T = y.shape[0]
+    y = y * torch.sigmoid(y)
+    q = y[:, :nqk].view(T, d.n_kv_heads, d.qk_dim)
+    k = y[:, nqk:2 * nqk].view(T, d.n_kv_heads, d.qk_dim)
+    q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + d.unit_eps) * d.qk_dim ** -0.5
+    k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + d.unit_eps)
+    beta = torch.sigmoid(proj[:, C + nv:C + nv + H].float())
+    g = torch.exp(-torch.exp(A_log.float()) * F.softplus(proj[:, C + nv + H:C + nv + 2 * H].float() + dt_bias.float()))
+    return torch.cat([q.reshape(T, nqk), k.reshape(T, nqk), y[:, 2 * nqk:], beta, g], -1).contiguous()
+
+
+def delta_prepare_ref(proj, conv_w, A_log, dt_bias, d, pos, conv_state, tok_slot, remain):
+    nqk, nv, H, C = _offsets(d)
+    taps = d.conv_taps
+    x = proj[:, :C].float()
+    cw = conv_w.float()
+    y = x * cw[:, taps - 1]
+    for back in range(1, taps):
+        prev = torch.zeros_like(x)
+        prev[back:] = x[:-back]
+        y = y + torch.where((pos.long() >= back).unsqueeze(-1), prev, torch.zeros_like(prev)) * cw[:, taps - 1 - back]
+    if conv_state is not None and taps > 1:
+        keep = (remain < taps - 1) & (tok_slot >= 0)
+        conv_state[tok_slot[keep].long(), (taps - 2 - remain[keep]).long()] = x[keep]
+    return _finish_prepare(y, proj, d, A_log, dt_bias)
+
+
+def delta_prepare(proj, conv_w, A_log, dt_bias, d, pos, conv_state=None, tok_slot=None, remain=None):
+    if use_native(proj) and d.conv_taps <= 8:
+        nqk, nv, H, C = _offsets(d)
+        u = torch.empty(proj.shape[0], C + 2 * H, dtype=torch.float32, device=proj.device)
+        keep = conv_state is not None and d.conv_taps > 1
+        lib().delta_prepare(proj, conv_w, A_log, dt_bias, u, pos, conv_state if keep else None, tok_slot if keep else None,
+                            remain if keep else None, None, d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim, d.conv_taps, d.unit_eps)
+        return u
+    return delta_prepare_ref(proj, conv_w, A_log, dt_bias, d, pos, conv_state, tok_slot, remain)
+
+
+def delta_prepare_step_ref(proj, conv_w, A_log, dt_bias, d, conv_state, slots):
+    nqk, nv, H, C = _offsets(d)
+    taps = d.conv_taps
+    x = proj[:, :C].float()
+    cw = conv_w.float()
+    y = x * cw[:, taps - 1]
+    if taps > 1:
+        idx = slots.long() if slots is not None else torch.arange(proj.shape[0], device=proj.device)
+        st = conv_state[idx]                                               # [B, taps - 1, C], oldest first
+        y = y + (st * cw[:, :taps - 1].t().unsqueeze(0)).sum(1)
+        conv_state[idx] = torch.cat([st[:, 1:], x.unsqueeze(1)], 1)
+    return _finish_prepare(y, proj, d, A_log, dt_bias)
+
+
+def delta_prepare_step(proj, conv_w, A_log, dt_bias, d, conv_state, slots):
+    if use_native(proj) and d.conv_taps <= 8:
+        nqk, nv, H, C = _offsets(d)
+        u = torch.empty(proj.shape[0], C + 2 * H, dtype=torch.float32, device=proj.device)
+        lib().delta_prepare(proj, conv_w, A_log, dt_bias, u, None, conv_state if d.conv_taps > 1 else None, None, None, slots,
+                            d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim, d.conv_taps, d.unit_eps)
+        return u
+    return delta_prepare_step_ref(proj, conv_w, A_log, dt_bias, d, conv_state, slots)
+
+
+def _split_u(u, d):
+    nqk, nv, H, C = _offsets(d)
+    T = u.shape[0]
+    return (u[:, :nqk].view(T, d.n_kv_heads, d.qk_dim), u[:, nqk:2 * nqk].view(T, d.n_kv_heads, d.qk_dim),
+            u[:, 2 * nqk:C].view(T, H, d.v_dim), u[:, C:C + H], u[:, C + H:C + 2 * H])
+
+
+def _delta_token(S, q, k, v, beta, g):
+    """S [H, d, dv]; q, k [H, d]; v [H, dv]; beta, g [H] -> (S', o [H, dv])."""
+    S = S * g.view(-1, 1, 1)
+    w = beta.view(-1, 1) * (v - torch.einsum("hdv,hd->hv", S, k))
+    S = S + k.unsqueeze(-1) * w.unsqueeze(1)
+    return S, torch.einsum("hdv,hd->hv", S, q)
+
+
+def delta_rule_scan_ref(u, d, cu_seqlens, s_state, slots):
+    q, k, v, beta, g = _split_u(u, d)
+    rep = d.n_heads // d.n_kv_heads
+    q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+    o = torch.zeros(u.shape[0], d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        S = torch.zeros(d.n_heads, d.qk_dim, d.v_dim, dtype=torch.float32, device=u.device)
+        for t in range(cu[b], cu[b + 1]):
+            S, o[t] = _delta_token(S, q[t], k[t], v[t], beta[t], g[t])
+        if s_state is not None and slots is not None and int(slots[b]) >= 0 and cu[b + 1] > cu[b]:
+            s_state[int(slots[b])] = S
+    return o
+
+
+def delta_rule_scan(u, d, cu_seqlens, s_state=None, slots=None):
+    """u [T, C + 2H] fp32 (see `delta_prepare`), sequences given by cu_seqlens, each from S = 0.  Returns o [T, H, dv] fp32; with
+    `s_state` and `slots` [n_seqs] int32, sequence b's final state is left in s_state[slots[b]] (slots[b] < 0: dropped)."""
+    if use_native(u) and d.qk_dim <= 256:
+        o = torch.empty(u.shape[0], d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
+        lib().delta_rule_scan(u, o, cu_seqlens, s_state, slots if s_state is not None else None, d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim)
+        return o
+    return delta_rule_scan_ref(u, d, cu_seqlens, s_state, slots)
+
+
+def delta_rule_step_ref(u, d, s_state, slots):
+    q, k, v, beta, g = _split_u(u, d)
+    rep = d.n_heads // d.n_kv_heads
+    q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+    o = torch.zeros(u.shape[0], d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
+    for b in range(u.shape[0]):
+        s = int(slots[b]) if slots is not None else b
+        s_state[s], o[b] = _delta_token(s_state[s], q[b], k[b], v[b], beta[b], g[b])
+    return o
+
+
+def delta_rule_step(u, d, s_state, slots):
+    """One token per row: s_state[slots[b]] (slots None: row b is slot b) is updated in place.  Returns o [B, H, dv] fp32."""
+    if use_native(u) and d.qk_dim <= 256:
+        o = torch.empty(u.shape[0], d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
+        lib().delta_rule_step(u, o, s_state, slots, d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim)
+        return o
+    return delta_rule_step_ref(u, d, s_state, slots)
+
+
+def gated_head_norm_ref(o, w, gate, eps, out_dtype):
+    T, H, dv = o.shape
+    n = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    gt = gate.float().view(T, H, dv)
+    return (n * gt * torch.sigmoid(gt)).reshape(T, H * dv).to(out_dtype)
+
+
+def gated_head_norm(o, w, gate, eps: float, out_dtype):
+    """o [T, H, dv] fp32, w [dv], gate [T, H * dv] (a column slice of the projection output; unit column stride)."""
+    if use_native(o):
+        out = torch.empty(o.shape[0], o.shape[1] * o.shape[2], dtype=out_dtype, device=o.device)
+        lib().gated_head_norm(o, w, gate, out, eps)
+        return out
+    return gated_head_norm_ref(o, w, gate, eps, out_dtype)
