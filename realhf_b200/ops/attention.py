@@ -437,7 +437,9 @@ def sink_window_attention(qkvg, v_n, a, temp, sink, pos, cu_seqlens, max_seqlen=
     if use_native(qkvg):
         T = qkvg.shape[0]
         out = torch.empty(T, a.n_heads * a.v_dim, dtype=qkvg.dtype, device=qkvg.device)
-        lib().sink_window_attention(qkvg, v_n, out, temp, sink, pos, a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim, a.scale,
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        lib().sink_window_attention(qkvg, v_n, out, temp, sink, cu_seqlens, max_seqlen, a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim, a.scale,
                                     a.window if a.window is not None else -1, a.keep_first,
                                     a.slope_base if a.slope_base is not None else -1.0, bool(a.out_gate))
         return out

@@ -306,7 +306,8 @@ void logprob_bwd_(Tensor logits, const Tensor& labels, const c10::optional<Tenso
 void register_gemm_ops(torch::Library& m);     // bindings_gemm.cpp
 void register_attn_ops(torch::Library& m);     // bindings_attn.cpp
 void register_comm_ops(torch::Library& m);
-void register_seq_ops(torch::Library& m);     // bindings_comm.cpp
+void register_seq_ops(torch::Library& m);      // bindings_seq.cpp
+void register_state_ops(torch::Library& m);    // bindings_state.cpp
 
 static int64_t set_pdl(int64_t on) { const int old = rb_get_pdl(); if (on >= 0) rb_set_pdl((int)on); return old; }
 
@@ -331,4 +332,5 @@ TORCH_LIBRARY(realhf_b200, m) {
   register_attn_ops(m);
   register_comm_ops(m);
   register_seq_ops(m);
+  register_state_ops(m);
 }

@@ -1,0 +1,226 @@
+// Gated delta rule (`DeltaRuleConfig`), packed (prefill) and one-token (decode) forms.  Per head, matrix state S [d, dv] in fp32:
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q          (the output is read after the update)
+// All arithmetic that enters the recurrence is fp32; exact expf / log1pf (compiled without fast-math).
+//
+//   delta_prepare    projection output `proj` [T, ld] = [q (G x d) | k (G x d) | v (H x dv) | gate (H x dv) | beta logits (H) | decay
+//                    inputs (H) | pad]  ->  u [T, C + 2H] fp32 = [q | k | v | beta | g],  C = 2 G d + H dv:
+//                    causal depthwise convolution (taps <= 8, weights [C, taps], tap taps - 1 meets the current token, inputs before a
+//                    sequence's first token are zero) + SiLU on the first C channels; q, k <- x / sqrt(sum x^2 + unit_eps) per head, q also times
+//                    d^-1/2; beta = sigmoid; g = exp(-exp(A_log) softplus(a + dt_bias)).  Packed form: earlier tokens are the
+//                    preceding rows (pos[t] tells how many belong to the sequence), and the last taps - 1 raw inputs of every
+//                    sequence go to conv_state [n_slots, taps - 1, C] (oldest first).  Step form (pos == null): earlier inputs
+//                    come from conv_state[slot], which is shifted by one.
+//   delta_rule       the recurrence.  A column of S depends only on its own v column, so columns are independent: a thread group of
+//                    LPC lanes owns one column (lane l holds rows e * LPC + l, 32 registers each), a CTA 128 / LPC columns of one
+//                    (sequence, head).  q, k, v, beta, g of 8 tokens at a time are staged in shared memory.  Packed form: S starts
+//                    at zero and the final S goes to s_state[slot]; step form: S is loaded from and stored to s_state[slot].
+//   gated_head_norm  o / sqrt(mean(o^2) + eps) * w * silu(gate) per (token, head) -> model type.
+#include "anytype.cuh"
+
+namespace {
+
+using rb::ld_any;
+using rb::st_any;
+
+constexpr int kMaxTaps = 8;
+
+__global__ void __launch_bounds__(256) delta_prepare_kernel(const void* __restrict__ proj, int64_t ld, int dt, const void* __restrict__ conv_w,
+                                                            const void* __restrict__ A_log, const void* __restrict__ dt_bias,
+                                                            float* __restrict__ u, const int* __restrict__ pos, float* __restrict__ conv_state,
+                                                            const int* __restrict__ tok_slot, const int* __restrict__ remain,
+                                                            const int* __restrict__ slots, int H, int G, int d, int dv, int taps,
+                                                            float unit_eps) {
+  extern __shared__ float ys[];               // [C] convolved + SiLU
+  const int64_t t = blockIdx.x;
+  const int nqk = G * d, nv = H * dv, C = 2 * nqk + nv, UW = C + 2 * H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const bool step = pos == nullptr;
+  const int p = step ? 0 : pos[t];
+  int slot = -1;
+  if (conv_state != nullptr) slot = step ? (slots ? slots[t] : (int)t) : tok_slot[t];
+  const int rem = (!step && conv_state != nullptr) ? remain[t] : 0;
+  float* st = (slot >= 0 && taps > 1) ? conv_state + (int64_t)slot * (taps - 1) * C : nullptr;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float x = ld_any(proj, dt, t * ld + c);
+    float y = x * ld_any(conv_w, dt, (int64_t)c * taps + taps - 1);
+    float hist[kMaxTaps - 1];
+#pragma unroll
+    for (int back = 1; back < kMaxTaps; ++back) {
+      if (back < taps) {
+        float xb;
+        if (step) xb = st ? st[(int64_t)(taps - 1 - back) * C + c] : 0.f;
+        else xb = back <= p ? ld_any(proj, dt, (t - back) * ld + c) : 0.f;
+        hist[back - 1] = xb;
+        y = fmaf(xb, ld_any(conv_w, dt, (int64_t)c * taps + taps - 1 - back), y);
+      }
+    }
+    if (st != nullptr) {
+      if (step) {           // shift: row i <- row i + 1, the newest row <- x (this thread owns channel c of the slot)
+#pragma unroll
+        for (int back = kMaxTaps - 1; back >= 1; --back)
+          if (back < taps) st[(int64_t)(taps - 1 - back) * C + c] = back == 1 ? x : hist[back - 2];
+      } else if (rem < taps - 1) {
+        st[(int64_t)(taps - 2 - rem) * C + c] = x;
+      }
+    }
+    ys[c] = y / (1.f + expf(-y));
+  }
+  __syncthreads();
+  // unit norms of the 2 G heads of q and k: one warp per head, fixed order
+  for (int hd = warp; hd < 2 * G; hd += nwarp) {
+    float ss = 0.f;
+    for (int e = lane; e < d; e += 32) { const float v = ys[hd * d + e]; ss += v * v; }
+    ss = rb::warp_sum(ss);
+    float r = 1.f / sqrtf(ss + unit_eps);
+    if (hd < G) r *= 1.f / sqrtf((float)d);
+    for (int e = lane; e < d; e += 32) u[t * UW + hd * d + e] = ys[hd * d + e] * r;
+  }
+  for (int c = 2 * nqk + threadIdx.x; c < C; c += blockDim.x) u[t * UW + c] = ys[c];
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float b = ld_any(proj, dt, t * ld + C + nv + h);
+    u[t * UW + C + h] = 1.f / (1.f + expf(-b));
+    const float a = ld_any(proj, dt, t * ld + C + nv + H + h) + ld_any(dt_bias, dt, h);
+    const float sp = a > 20.f ? a : log1pf(expf(a));
+    u[t * UW + C + H + h] = expf(-expf(ld_any(A_log, dt, h)) * sp);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ recurrence
+constexpr int kScanThreads = 128, kEPL = 32, kTok = 8;
+
+struct ScanParams {
+  const float* u; float* o;
+  const int* cu;            // packed form: [n_seqs + 1]; step form: null (sequence b = row b, one token)
+  float* s_state;           // [n_slots, H, d, dv] or null
+  const int* slots;         // per sequence / row; null = identity (step form) or no state (packed form)
+  int H, G, d, dv, step;
+};
+
+template <int LPC>
+__global__ void __launch_bounds__(kScanThreads) delta_rule_kernel(ScanParams p) {
+  constexpr int NCOL = kScanThreads / LPC;
+  extern __shared__ float sm[];
+  const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * NCOL;
+  const int g = h / (p.H / p.G), d = p.d, dv = p.dv;
+  const int nqk = p.G * d, C = 2 * nqk + p.H * dv, UW = C + 2 * p.H;
+  const int tid = threadIdx.x, l = tid % LPC, col = c0 + tid / LPC;
+  const bool active = col < dv;
+  int t0, t1;
+  if (p.step) { t0 = seq; t1 = seq + 1; } else { t0 = p.cu[seq]; t1 = p.cu[seq + 1]; }
+  if (t1 <= t0) return;
+  const int slot = p.s_state == nullptr ? -1 : (p.slots ? p.slots[seq] : (p.step ? seq : -1));
+  float* S_g = slot >= 0 ? p.s_state + (((int64_t)slot * p.H + h) * d) * dv : nullptr;
+  const int dpad = kEPL * LPC;                    // rows e * LPC + l; rows >= d hold zeros and read zero q / k
+  float* qs = sm;                                 // [kTok][dpad]
+  float* ks = qs + kTok * dpad;                   // [kTok][dpad]
+  float* vs = ks + kTok * dpad;                   // [kTok][NCOL]
+  float* bg = vs + kTok * NCOL;                   // [kTok][2]  beta, g
+  float S[kEPL];
+#pragma unroll
+  for (int e = 0; e < kEPL; ++e) {
+    const int row = e * LPC + l;
+    S[e] = (p.step && S_g && active && row < d) ? S_g[(int64_t)row * dv + col] : 0.f;
+  }
+  for (int tb = t0; tb < t1; tb += kTok) {
+    const int nt = min(kTok, t1 - tb);
+    __syncthreads();
+    for (int idx = tid; idx < nt * dpad; idx += kScanThreads) {
+      const int tt = idx / dpad, e = idx % dpad;
+      const float* row = p.u + (int64_t)(tb + tt) * UW;
+      qs[idx] = e < d ? row[g * d + e] : 0.f;
+      ks[idx] = e < d ? row[nqk + g * d + e] : 0.f;
+    }
+    for (int idx = tid; idx < nt * NCOL; idx += kScanThreads) {
+      const int tt = idx / NCOL, c = c0 + idx % NCOL;
+      vs[idx] = c < dv ? p.u[(int64_t)(tb + tt) * UW + 2 * nqk + h * dv + c] : 0.f;
+    }
+    if (tid < nt * 2) bg[tid] = p.u[(int64_t)(tb + tid / 2) * UW + C + (tid & 1) * p.H + h];
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float beta = bg[tt * 2], gg = bg[tt * 2 + 1];
+      const float* kq = ks + tt * dpad + l;
+      const float* qq = qs + tt * dpad + l;
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < kEPL; ++e) { S[e] *= gg; acc = fmaf(S[e], kq[e * LPC], acc); }
+#pragma unroll
+      for (int off = 1; off < LPC; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      const float w = beta * (vs[tt * NCOL + tid / LPC] - acc);
+      float ov = 0.f;
+#pragma unroll
+      for (int e = 0; e < kEPL; ++e) { S[e] = fmaf(kq[e * LPC], w, S[e]); ov = fmaf(S[e], qq[e * LPC], ov); }
+#pragma unroll
+      for (int off = 1; off < LPC; off <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, off);
+      if (active && l == 0) p.o[((int64_t)(tb + tt) * p.H + h) * dv + col] = ov;
+    }
+  }
+  if (S_g && active) {
+#pragma unroll
+    for (int e = 0; e < kEPL; ++e) {
+      const int row = e * LPC + l;
+      if (row < d) S_g[(int64_t)row * dv + col] = S[e];
+    }
+  }
+}
+
+// one warp per (token, head)
+__global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __restrict__ o, const void* __restrict__ w, int dtw,
+                                                              const void* __restrict__ gate, int64_t ldg, int dtg, void* __restrict__ out, int dto,
+                                                              int64_t rows, int H, int dv, float eps) {
+  const int64_t r = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = r / H;
+  const int h = (int)(r % H);
+  const float* x = o + r * dv;
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) ss += x[c] * x[c];
+  ss = rb::warp_sum(ss);
+  const float rs = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int c = lane; c < dv; c += 32) {
+    const float gt = ld_any(gate, dtg, t * ldg + h * dv + c);
+    st_any(out, dto, r * dv + c, x[c] * rs * ld_any(w, dtw, c) * (gt / (1.f + expf(-gt))));
+  }
+}
+
+}  // namespace
+
+extern "C" int rb_delta_prepare(const void* proj, int64_t ld, int dt, const void* conv_w, const void* A_log, const void* dt_bias, float* u,
+                                const int* pos, float* conv_state, const int* tok_slot, const int* remain, const int* slots, int64_t T, int H, int G,
+                                int d, int dv, int taps, float unit_eps, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (taps < 1 || taps > kMaxTaps) return -1;
+  const int C = 2 * G * d + H * dv;
+  const size_t smem = sizeof(float) * (size_t)C;
+  if (smem > 200 * 1024) return -2;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  delta_prepare_kernel<<<(unsigned)T, 256, smem, s>>>(proj, ld, dt, conv_w, A_log, dt_bias, u, pos, conv_state, tok_slot, remain, slots, H, G, d, dv,
+                                                      taps, unit_eps);
+  return 0;
+}
+
+extern "C" int rb_delta_rule(const float* u, float* o, const int* cu, float* s_state, const int* slots, int n_seqs, int H, int G, int d, int dv,
+                             int step, cudaStream_t s) {
+  if (n_seqs == 0) return 0;
+  if (d > 8 * kEPL || H % G) return -1;
+  const int lpc = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8;
+  const int ncol = kScanThreads / lpc;
+  ScanParams p{u, o, cu, s_state, slots, H, G, d, dv, step};
+  const size_t smem = sizeof(float) * ((size_t)2 * kTok * kEPL * lpc + (size_t)kTok * ncol + 2 * kTok);
+  dim3 grid(n_seqs, H, RB_CEIL_DIV(dv, ncol));
+  switch (lpc) {
+    case 1: delta_rule_kernel<1><<<grid, kScanThreads, smem, s>>>(p); break;
+    case 2: delta_rule_kernel<2><<<grid, kScanThreads, smem, s>>>(p); break;
+    case 4: delta_rule_kernel<4><<<grid, kScanThreads, smem, s>>>(p); break;
+    default: delta_rule_kernel<8><<<grid, kScanThreads, smem, s>>>(p); break;
+  }
+  return 0;
+}
+
+extern "C" int rb_gated_head_norm(const float* o, const void* w, int dtw, const void* gate, int64_t ldg, int dtg, void* out, int dto, int64_t T, int H,
+                                  int dv, float eps, cudaStream_t s) {
+  const int64_t rows = T * H;
+  if (rows == 0) return 0;
+  gated_head_norm_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(o, w, dtw, gate, ldg, dtg, out, dto, rows, H, dv, eps);
+  return 0;
+}

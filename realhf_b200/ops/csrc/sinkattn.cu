@@ -1,0 +1,398 @@
+// Window attention with a sink (`WindowAttentionConfig`): grouped key / value heads, no rotation.
+//
+//   score(i, j) = q_i . k_j * scale * temp_h - slope_h * (i - j),   slope_h = 2^(-slope_base (h + 1) / H)
+//   visible:      j <= i and (i - j < window or j < keep_first)                (window < 0: every j <= i)
+//   weights:      exp(score - m) / (sum_visible exp(score - m) + exp(sink_h - m))   (the sink is a bare logit: key-less, value-less)
+//   output:       sum_j w_ij vhat_j * sigmoid(gate_h),   vhat = v / sqrt(mean(v^2) + eps) per head (cached so)
+//
+// Everything is fp32 arithmetic whatever the storage type (a type code per launch: 0 fp32, 1 bf16, 2 fp16); exact expf (compiled
+// without fast-math).  The projection output `qkvg` [T, ld] holds [q (H x d) | k (G x d) | v (G x dv) | gate logits] per row.
+// Caches: kc [n_slots, G, rows, d], vc [n_slots, G, rows, dv]; position p lives in row p when p < keep_first, else in row
+// keep_first + (p - keep_first) % (rows - keep_first).
+//
+//   value_norm_store       packed prefill: vhat -> [T, G * dv], and the rows a later decode step can still see -> caches
+//   sink_window_prefill    packed prefill over the batch's own keys: CTA = 32 queries x 1 head of one sequence, 32-key tiles in
+//                          shared memory, online softmax whose running maximum starts at the sink (denominator 1)
+//   sink_window_decode     one token per row: CTA = (row, kv head) serving the group's query heads; appends k / vhat, then walks the
+//                          visible cache rows in 128-key tiles (one key per thread for the scores, one column per thread for P.V)
+#include "anytype.cuh"
+
+namespace {
+
+using rb::ld_any;
+using rb::st_any;
+
+RB_DEVICE int cache_row(int p, int keep, int rows) {
+  const int ring = max(rows - keep, 1);
+  return p < keep ? p : keep + (p - keep) % ring;
+}
+
+// ------------------------------------------------------------------------------------------------ value norm + cache fill
+// one CTA per token; a warp per kv head (looping)
+__global__ void __launch_bounds__(128) value_norm_store_kernel(const void* __restrict__ qkvg, int64_t ld, int dt, void* __restrict__ vout,
+                                                                void* __restrict__ kc, void* __restrict__ vc, const int* __restrict__ tok_slot,
+                                                                const int* __restrict__ pos, const int* __restrict__ remain, int H, int G, int d,
+                                                                int dv, int keep, int rows, int do_norm, float eps) {
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int64_t base = t * ld;
+  const int ok = H * d, ov = ok + G * d;
+  int slot = -1, row = 0;
+  if (kc != nullptr) {
+    slot = tok_slot[t];
+    const int p = pos[t];
+    if (slot >= 0 && !(p < keep || remain[t] < rows - keep)) slot = -1;   // a row that a later position of this prompt overwrites
+    row = cache_row(p, keep, rows);
+  }
+  for (int g = warp; g < G; g += nwarp) {
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) { const float v = ld_any(qkvg, dt, base + ov + g * dv + c); ss += v * v; }
+    ss = rb::warp_sum(ss);
+    const float r = do_norm ? 1.f / sqrtf(ss / (float)dv + eps) : 1.f;
+    const int64_t crow = slot >= 0 ? ((int64_t)slot * G + g) * rows + row : 0;
+    for (int c = lane; c < dv; c += 32) {
+      const float v = ld_any(qkvg, dt, base + ov + g * dv + c) * r;
+      st_any(vout, dt, t * (int64_t)(G * dv) + g * dv + c, v);
+      if (slot >= 0) st_any(vc, dt, crow * dv + c, v);
+    }
+    if (slot >= 0)
+      for (int c = lane; c < d; c += 32) st_any(kc, dt, crow * d + c, ld_any(qkvg, dt, base + ok + g * d + c));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ packed prefill
+constexpr int BQ = 32, BK = 32, kPfThreads = 128;
+
+struct PrefillParams {
+  const void* qkvg; int64_t ld;
+  const void* vn;            // [T, G * dv]
+  void* out;                 // [T, H * dv]
+  const void* temp; const void* sink;   // [H] in the model type, or null
+  const int* cu;             // [n_seqs + 1]
+  int H, G, d, dv, window, keep, gate, dt;
+  float scale, slope_base;
+};
+
+// NJ = ceil(dv / 32): a thread owns 2 query rows x NJ float4 column groups of the output tile
+template <int NJ>
+__global__ void __launch_bounds__(kPfThreads) sink_window_prefill_kernel(PrefillParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int seq = blockIdx.y, h = blockIdx.z, g = h / (p.H / p.G);
+  const int s0 = p.cu[seq], L = p.cu[seq + 1] - s0;
+  const int q0 = blockIdx.x * BQ;
+  if (q0 >= L) return;
+  const int d = p.d, dv = p.dv, dp = (d + 3) & ~3, dvp = NJ * 32;
+  const int qs = dp + 4, vs = dvp + 4;                // padded row strides (floats): conflict-free float4 reads
+  float* Qs = smem;                                   // [BQ][qs]
+  float* Ks = Qs + BQ * qs;                           // [BK][qs]
+  float* Vs = Ks + BK * qs;                           // [BK][vs]
+  float* Ps = Vs + BK * vs;                           // [BQ][BK + 1]
+  const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;   // tx: keys tx + 8c of a tile / float4 output groups; ty: 2 query rows
+  const int nq = min(BQ, L - q0);
+  const int dt = p.dt;
+  const int ok = p.H * d;
+
+  for (int idx = tid; idx < BQ * dp; idx += kPfThreads) {
+    const int r = idx / dp, e = idx % dp;
+    Qs[r * qs + e] = (r < nq && e < d) ? ld_any(p.qkvg, dt, (int64_t)(s0 + q0 + r) * p.ld + h * d + e) : 0.f;
+  }
+  const float qmul = p.scale * (p.temp ? ld_any(p.temp, dt, h) : 1.f);
+  const float slope = p.slope_base >= 0.f ? exp2f(-p.slope_base * (float)(h + 1) / (float)p.H) : 0.f;
+  float m[2], l[2], o[2][NJ][4];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (p.sink) { m[r] = ld_any(p.sink, dt, h); l[r] = 1.f; } else { m[r] = -INFINITY; l[r] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[r][j][c] = 0.f;
+  }
+  // key ranges of this query tile: the kept first tokens [0, ka) and the window part [lo, q_last]
+  const int q_last = q0 + nq - 1;
+  const int lo = p.window < 0 ? 0 : max(0, q0 - p.window + 1);
+  const int ka = p.window < 0 ? 0 : min(p.keep, lo);
+  const int lo_al = lo / BK * BK;                       // window tiles start on a tile border
+  const int n_keep_tiles = RB_CEIL_DIV(min(ka, lo_al), BK);   // keys of [0, ka) below lo_al (the rest falls into window tiles)
+  const int n_win_tiles = RB_CEIL_DIV(q_last + 1 - lo_al, BK);
+
+  for (int tile = 0; tile < n_keep_tiles + n_win_tiles; ++tile) {
+    const int k0 = tile < n_keep_tiles ? tile * BK : lo_al + (tile - n_keep_tiles) * BK;
+    const int kend = tile < n_keep_tiles ? min(ka, lo_al) : q_last + 1;   // keys at or beyond kend are not loaded
+    __syncthreads();
+    for (int idx = tid; idx < BK * dp; idx += kPfThreads) {
+      const int r = idx / dp, e = idx % dp;
+      Ks[r * qs + e] = (k0 + r < kend && e < d) ? ld_any(p.qkvg, dt, (int64_t)(s0 + k0 + r) * p.ld + ok + g * d + e) : 0.f;
+    }
+    for (int idx = tid; idx < BK * dvp; idx += kPfThreads) {
+      const int r = idx / dvp, e = idx % dvp;
+      Vs[r * vs + e] = (k0 + r < kend && e < dv) ? ld_any(p.vn, dt, (int64_t)(s0 + k0 + r) * (p.G * dv) + g * dv + e) : 0.f;
+    }
+    __syncthreads();
+    // scores of 2 rows x 4 keys
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    for (int e = 0; e < dp; e += 4) {
+      const float4 qa = *reinterpret_cast<const float4*>(Qs + (ty * 2) * qs + e);
+      const float4 qb = *reinterpret_cast<const float4*>(Qs + (ty * 2 + 1) * qs + e);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float4 kk = *reinterpret_cast<const float4*>(Ks + (tx + 8 * c) * qs + e);
+        s[0][c] = fmaf(qa.x, kk.x, fmaf(qa.y, kk.y, fmaf(qa.z, kk.z, fmaf(qa.w, kk.w, s[0][c]))));
+        s[1][c] = fmaf(qb.x, kk.x, fmaf(qb.y, kk.y, fmaf(qb.z, kk.z, fmaf(qb.w, kk.w, s[1][c]))));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int i = q0 + ty * 2 + r;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = k0 + tx + 8 * c;
+        const bool vis = j < kend && j <= i && i <= q_last && (p.window < 0 || i - j < p.window || j < p.keep);
+        s[r][c] = vis ? s[r][c] * qmul - slope * (float)(i - j) : -INFINITY;
+        mx = fmaxf(mx, s[r][c]);
+      }
+#pragma unroll
+      for (int off = 1; off < 8; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float mn = fmaxf(m[r], mx);
+      const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mn);
+      float ps = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float pr = (s[r][c] == -INFINITY) ? 0.f : expf(s[r][c] - mn);
+        Ps[(ty * 2 + r) * (BK + 1) + tx + 8 * c] = pr;
+        ps += pr;
+      }
+#pragma unroll
+      for (int off = 1; off < 8; off <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+      l[r] = l[r] * corr + ps;
+      m[r] = mn;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[r][j][c] *= corr;
+    }
+    __syncwarp();   // a row's 8 score lanes and its 8 output lanes are the same lanes of one warp
+    const int nk = min(BK, kend - k0);
+    for (int kk = 0; kk < nk; ++kk) {
+      const float pa = Ps[(ty * 2) * (BK + 1) + kk], pb = Ps[(ty * 2 + 1) * (BK + 1) + kk];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const float4 v = *reinterpret_cast<const float4*>(Vs + kk * vs + j * 32 + tx * 4);
+        o[0][j][0] = fmaf(pa, v.x, o[0][j][0]); o[0][j][1] = fmaf(pa, v.y, o[0][j][1]);
+        o[0][j][2] = fmaf(pa, v.z, o[0][j][2]); o[0][j][3] = fmaf(pa, v.w, o[0][j][3]);
+        o[1][j][0] = fmaf(pb, v.x, o[1][j][0]); o[1][j][1] = fmaf(pb, v.y, o[1][j][1]);
+        o[1][j][2] = fmaf(pb, v.z, o[1][j][2]); o[1][j][3] = fmaf(pb, v.w, o[1][j][3]);
+      }
+    }
+  }
+  const int og = p.H * d + p.G * d + p.G * dv;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = q0 + ty * 2 + r;
+    if (i > q_last) continue;
+    const int64_t t = s0 + i;
+    float f = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    if (p.gate) f *= 1.f / (1.f + expf(-ld_any(p.qkvg, dt, t * p.ld + og + h)));
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int col = j * 32 + tx * 4 + c;
+        if (col < dv) st_any(p.out, dt, t * (int64_t)(p.H * dv) + h * dv + col, o[r][j][c] * f);
+      }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ decode
+constexpr int kDecThreads = 128, kMaxRep = 8, kMaxColsPerThread = 2;   // dv <= 256
+
+struct DecodeParams {
+  const void* qkvg; int64_t ld;
+  void* out; const void* temp; const void* sink;
+  void* kc; void* vc;
+  const int* lens; const int* slots;
+  int H, G, d, dv, rows, window, keep, gate, do_norm, dt;
+  float scale, slope_base, eps;
+};
+
+__global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int b = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rep = p.H / p.G, d = p.d, dv = p.dv, dt = p.dt;
+  float* qs = smem;                         // [rep][d], scaled by scale * temp
+  float* ps = qs + rep * d;                 // [rep][kDecThreads]
+  float* red = ps + rep * kDecThreads;      // [rep][4] warp partials, then [rep] results at red + rep * 4
+  float* vnew = red + rep * 5;              // [dv]
+  int* rws = reinterpret_cast<int*>(vnew + dv);   // [kDecThreads] cache rows of the tile's keys
+  const int slot = p.slots ? p.slots[b] : b;
+  const int n = p.lens[slot];               // the new token's position
+  const int64_t base = (int64_t)b * p.ld;
+  const int ok = p.H * d, ov = ok + p.G * d, og = ov + p.G * dv;
+  const int64_t cbase = ((int64_t)slot * p.G + g) * p.rows;
+
+  for (int idx = tid; idx < rep * d; idx += kDecThreads) {
+    const int h = g * rep + idx / d;
+    qs[idx] = ld_any(p.qkvg, dt, base + h * d + idx % d) * (p.scale * (p.temp ? ld_any(p.temp, dt, h) : 1.f));
+  }
+  // append the new key and normalised value (fp32 statistics; the stored value is what later steps read)
+  {
+    float ss = 0.f;
+    for (int c = tid; c < dv; c += kDecThreads) { const float v = ld_any(p.qkvg, dt, base + ov + g * dv + c); vnew[c] = v; ss += v * v; }
+    ss = rb::block_reduce<false>(ss, red);
+    const float r = p.do_norm ? 1.f / sqrtf(ss / (float)dv + p.eps) : 1.f;
+    const int64_t row = cbase + cache_row(n, p.keep, p.rows);
+    for (int c = tid; c < dv; c += kDecThreads) st_any(p.vc, dt, row * dv + c, vnew[c] * r);
+    for (int c = tid; c < d; c += kDecThreads) st_any(p.kc, dt, row * d + c, ld_any(p.qkvg, dt, base + ok + g * d + c));
+  }
+  __syncthreads();   // the CTA's own global writes are visible to its threads from here on
+
+  const int lo = p.window < 0 ? 0 : max(0, n - p.window + 1);
+  const int ka = p.window < 0 ? 0 : min(p.keep, lo);
+  const int nk = ka + (n - lo + 1);         // visible keys: positions [0, ka) and [lo, n]
+  float m[kMaxRep], l[kMaxRep], acc[kMaxRep][kMaxColsPerThread];
+#pragma unroll
+  for (int r = 0; r < kMaxRep; ++r) {
+    if (r < rep && p.sink) { m[r] = ld_any(p.sink, dt, g * rep + r); l[r] = 1.f; } else { m[r] = -INFINITY; l[r] = 0.f; }
+#pragma unroll
+    for (int c = 0; c < kMaxColsPerThread; ++c) acc[r][c] = 0.f;
+  }
+  const bool vec_k = (d % 4 == 0);
+  for (int t0 = 0; t0 < nk; t0 += kDecThreads) {
+    const int idx = t0 + tid;
+    const bool have = idx < nk;
+    const int j = have ? (idx < ka ? idx : lo + idx - ka) : 0;
+    float s[kMaxRep];
+#pragma unroll
+    for (int r = 0; r < kMaxRep; ++r) s[r] = 0.f;
+    if (have) {
+      const int jr = cache_row(j, p.keep, p.rows);
+      rws[tid] = jr;
+      const int64_t krow = (cbase + jr) * d;
+      if (vec_k) {
+        for (int e = 0; e < d; e += 4) {
+          const float4 kk = rb::ld4_any(p.kc, dt, krow + e);
+#pragma unroll
+          for (int r = 0; r < kMaxRep; ++r)
+            if (r < rep) {
+              const float4 qq = *reinterpret_cast<const float4*>(qs + r * d + e);
+              s[r] = fmaf(qq.x, kk.x, fmaf(qq.y, kk.y, fmaf(qq.z, kk.z, fmaf(qq.w, kk.w, s[r]))));
+            }
+        }
+      } else {
+        for (int e = 0; e < d; ++e) {
+          const float kk = ld_any(p.kc, dt, krow + e);
+#pragma unroll
+          for (int r = 0; r < kMaxRep; ++r)
+            if (r < rep) s[r] = fmaf(qs[r * d + e], kk, s[r]);
+        }
+      }
+    }
+    // tile maximum per head -> running maximum, weights into shared memory
+#pragma unroll
+    for (int r = 0; r < kMaxRep; ++r)
+      if (r < rep) {
+        const float slope = p.slope_base >= 0.f ? exp2f(-p.slope_base * (float)(g * rep + r + 1) / (float)p.H) : 0.f;
+        s[r] = have ? s[r] - slope * (float)(n - j) : -INFINITY;
+        const float wm = rb::warp_max(s[r]);
+        if (lane == 0) red[r * 4 + warp] = wm;
+      }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kMaxRep; ++r)
+      if (r < rep) {
+        const float tm = fmaxf(fmaxf(red[r * 4], red[r * 4 + 1]), fmaxf(red[r * 4 + 2], red[r * 4 + 3]));
+        const float mn = fmaxf(m[r], tm);
+        const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mn);
+        const float pr = have ? expf(s[r] - mn) : 0.f;
+        ps[r * kDecThreads + tid] = pr;
+        l[r] *= corr;
+#pragma unroll
+        for (int c = 0; c < kMaxColsPerThread; ++c) acc[r][c] *= corr;
+        m[r] = mn;
+      }
+    __syncthreads();
+    const int cnt = min(kDecThreads, nk - t0);
+    // denominators: every thread adds the tile's weights in the same order (no second reduction needed)
+#pragma unroll
+    for (int r = 0; r < kMaxRep; ++r)
+      if (r < rep) {
+        float sum = 0.f;
+        for (int k = 0; k < cnt; ++k) sum += ps[r * kDecThreads + k];
+        l[r] += sum;
+      }
+    for (int k = 0; k < cnt; ++k) {
+      const int64_t vrow = (cbase + rws[k]) * dv;
+#pragma unroll
+      for (int c = 0; c < kMaxColsPerThread; ++c) {
+        const int col = tid + c * kDecThreads;
+        if (col < dv) {
+          const float v = ld_any(p.vc, dt, vrow + col);
+#pragma unroll
+          for (int r = 0; r < kMaxRep; ++r)
+            if (r < rep) acc[r][c] = fmaf(ps[r * kDecThreads + k], v, acc[r][c]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < kMaxRep; ++r)
+    if (r < rep) {
+      const int h = g * rep + r;
+      float f = l[r] > 0.f ? 1.f / l[r] : 0.f;
+      if (p.gate) f *= 1.f / (1.f + expf(-ld_any(p.qkvg, dt, base + og + h)));
+#pragma unroll
+      for (int c = 0; c < kMaxColsPerThread; ++c) {
+        const int col = tid + c * kDecThreads;
+        if (col < dv) st_any(p.out, dt, (int64_t)b * (p.H * dv) + h * dv + col, acc[r][c] * f);
+      }
+    }
+}
+
+}  // namespace
+
+extern "C" int rb_value_norm_store(const void* qkvg, int64_t ld, int dt, void* vout, void* kc, void* vc, const int* tok_slot, const int* pos,
+                                   const int* remain, int64_t T, int H, int G, int d, int dv, int keep, int rows, int do_norm, float eps,
+                                   cudaStream_t s) {
+  if (T == 0) return 0;
+  value_norm_store_kernel<<<(unsigned)T, 128, 0, s>>>(qkvg, ld, dt, vout, kc, vc, tok_slot, pos, remain, H, G, d, dv, keep, rows, do_norm, eps);
+  return 0;
+}
+
+extern "C" int rb_sink_window_prefill(const void* qkvg, int64_t ld, const void* vn, void* out, const void* temp, const void* sink, const int* cu,
+                                      int n_seqs, int max_seqlen, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base,
+                                      int gate, int dt, cudaStream_t s) {
+  if (n_seqs == 0 || max_seqlen == 0) return 0;
+  if (dv > 256 || d > 512 || H % G) return -1;
+  PrefillParams p{qkvg, ld, vn, out, temp, sink, cu, H, G, d, dv, window, keep, gate, dt, scale, slope_base};
+  const int nj = dv <= 32 ? 1 : dv <= 64 ? 2 : dv <= 128 ? 4 : 8;
+  const int dp = (d + 3) & ~3;
+  const size_t smem = sizeof(float) * ((size_t)(BQ + BK) * (dp + 4) + (size_t)BK * (nj * 32 + 4) + (size_t)BQ * (BK + 1));
+  dim3 grid(RB_CEIL_DIV(max_seqlen, BQ), n_seqs, H);
+#define RB_L(NJ)                                                                                                          \
+  {                                                                                                                       \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(sink_window_prefill_kernel<NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    sink_window_prefill_kernel<NJ><<<grid, kPfThreads, smem, s>>>(p);                                                     \
+  }
+  switch (nj) {
+    case 1: RB_L(1); break;
+    case 2: RB_L(2); break;
+    case 4: RB_L(4); break;
+    default: RB_L(8); break;
+  }
+#undef RB_L
+  return 0;
+}
+
+extern "C" int rb_sink_window_decode(const void* qkvg, int64_t ld, void* out, const void* temp, const void* sink, void* kc, void* vc,
+                                     const int* lens, const int* slots, int B, int H, int G, int d, int dv, int rows, float scale, int window,
+                                     int keep, float slope_base, int gate, int do_norm, float eps, int dt, cudaStream_t s) {
+  if (B == 0) return 0;
+  const int rep = H / G;
+  if (H % G || rep > kMaxRep || dv > kDecThreads * kMaxColsPerThread) return -1;
+  DecodeParams p{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, dv, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps};
+  const size_t smem = sizeof(float) * ((size_t)rep * d + (size_t)rep * kDecThreads + rep * 5 + 32 + dv + kDecThreads);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(sink_window_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  sink_window_decode_kernel<<<dim3(B, G), kDecThreads, smem, s>>>(p);
+  return 0;
+}
