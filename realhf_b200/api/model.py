@@ -278,22 +278,25 @@ class ReaLModelConfig:
         h, f, v = self.hidden_dim, self.intermediate_dim, self.vocab_size
         if self.blocks is not None:
             n = 2 * v * h + h
+            norms = (2 if self.sandwich_norm else 1) + self.conv_taps       # per sublayer: norm(s) and convolution taps, times h
             for b in self.blocks:
                 if b.mixer == "window_attention":
                     a = b.wattn
-                    n += h * (a.n_heads * a.qk_dim + a.n_kv_heads * (a.qk_dim + a.v_dim) + a.n_heads) + a.n_heads * a.v_dim * h + h
+                    qkv = a.n_heads * a.qk_dim + a.n_kv_heads * (a.qk_dim + a.v_dim)
+                    n += h * (qkv + (a.n_heads if a.out_gate else 0)) + (qkv if a.qkv_bias else 0) + a.n_heads * a.v_dim * h
+                    n += a.n_heads * (int(a.head_temp) + int(a.sink)) + norms * h
                 elif b.mixer == "delta":
                     a = b.delta
-                    n += h * (2 * a.n_kv_heads * a.qk_dim + 2 * a.n_heads * a.v_dim + 2 * a.n_heads) + a.n_heads * a.v_dim * h + h
-                    n += a.conv_channels * a.conv_taps
+                    n += h * (2 * a.n_kv_heads * a.qk_dim + 2 * a.n_heads * a.v_dim + 2 * a.n_heads) + a.n_heads * a.v_dim * h
+                    n += a.conv_channels * a.conv_taps + 2 * a.n_heads + a.v_dim + norms * h
                 else:
                     a = b.attn
                     n += h * a.n_heads * a.qk_dim + (h * a.kv_rank + a.kv_rank if a.kv_from is None else 0)
-                    n += a.kv_rank * a.n_heads * (a.qk_dim + a.v_dim) + a.n_heads * a.v_dim * h + (2 + self.conv_taps) * h
+                    n += a.kv_rank * a.n_heads * (a.qk_dim + a.v_dim) + a.n_heads * a.v_dim * h + norms * h
                 if b.mlp is not None:
                     e = b.mlp.moe.num_experts if b.mlp.kind == "moe" else 1
                     mats = 2 if b.mlp.kind == "relu2" else 3
-                    n += e * mats * h * b.mlp.ff + (e * (h + 1) if b.mlp.kind == "moe" else 0) + (2 + self.conv_taps) * h
+                    n += e * mats * h * b.mlp.ff + (e * (h + 1) if b.mlp.kind == "moe" else 0) + norms * h
             if self.loop is not None and self.loop.inject:
                 n += 2 * h * h
             return n

@@ -711,8 +711,8 @@ def softcap_logits(logits, cap: Optional[float]):
 
 
 def sinusoid_inv_freq(width: int, base: float, device) -> torch.Tensor:
-    """fp32 [width // 2]: base^(-2i / width), rounded once from float64."""
-    i = torch.arange(width // 2, dtype=torch.float64)
+    """fp32 [ceil(width / 2)]: base^(-2i / width), rounded once from float64."""
+    i = torch.arange((width + 1) // 2, dtype=torch.float64)
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / width).float().to(device)
 
 
@@ -720,7 +720,7 @@ def embed_sinusoid_ref(ids, wte, pos, inv_freq):
     ang = pos.float().unsqueeze(1) * inv_freq.unsqueeze(0)            # fp32 product, as the kernel forms it
     x = F.embedding(ids.long(), wte).float()
     x[:, 0::2] += torch.sin(ang)
-    x[:, 1::2] += torch.cos(ang)
+    x[:, 1::2] += torch.cos(ang[:, : x.shape[1] // 2])
     return x
 
 

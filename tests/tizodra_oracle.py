@@ -28,11 +28,11 @@ def rms_norm(x, w, eps):
 def sinusoid(T: int, width: int) -> torch.Tensor:
     """[T, width] of interleaved pairs: out[:, 2i] = sin(a_i), out[:, 2i + 1] = cos(a_i), a_i = p / 10000^(2i / width)."""
     p = torch.arange(T, dtype=F64).unsqueeze(1)
-    i = torch.arange(width // 2, dtype=F64).unsqueeze(0)
+    i = torch.arange((width + 1) // 2, dtype=F64).unsqueeze(0)
     ang = p * torch.pow(torch.tensor(10000.0, dtype=F64), -2.0 * i / width)
     out = torch.zeros(T, width, dtype=F64)
     out[:, 0::2] = torch.sin(ang)
-    out[:, 1::2] = torch.cos(ang)
+    out[:, 1::2] = torch.cos(ang[:, : width // 2])
     return out
 
 
@@ -50,19 +50,14 @@ def visible(T: int, size: Optional[int], keep_first: int) -> torch.Tensor:
     return ok
 
 
-def attention_mixer(sd, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch.Tensor:
-    T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    w = lambda n: sd[pre + n].to(F64)
-    q = (h @ w("q").T + w("q.b")).view(T, H, d)
-    k = (h @ w("k").T + w("k.b")).view(T, G, d)
-    v = rms_divide((h @ w("v").T + w("v.b")).view(T, G, dv), eps)
-    gate = torch.sigmoid(h @ w("g").T)                       # [T, H]
+def attention_core(q, k, v, gate, m: dict, temp, sink) -> torch.Tensor:
+    """q [T, H, d], k [T, G, d], v [T, G, dv] (already normalised), gate [T, H] or None (already a sigmoid), temp / sink [H] -> [T, H, dv]."""
+    T, H, _ = q.shape
+    G, dv = k.shape[1], v.shape[2]
     mask = m.get("mask")
     ok = visible(T, mask["size"] if mask else None, (mask or {}).get("keep_first", 0))
     dist = (torch.arange(T).unsqueeze(1) - torch.arange(T).unsqueeze(0)).to(F64)
     out = torch.zeros(T, H, dv, dtype=F64)
-    temp, sink = w("temp"), w("sink")
     for hh in range(H):
         g = hh // (H // G)
         slope = 2.0 ** (-8.0 * (hh + 1) / H)
@@ -71,7 +66,21 @@ def attention_mixer(sd, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch
         mx = torch.maximum(s.max(-1, keepdim=True).values, sink[hh])
         e = torch.exp(s - mx)
         den = e.sum(-1, keepdim=True) + torch.exp(sink[hh] - mx)
-        out[:, hh] = ((e / den) @ v[:, g]) * gate[:, hh:hh + 1]
+        out[:, hh] = (e / den) @ v[:, g]
+        if gate is not None:
+            out[:, hh] = out[:, hh] * gate[:, hh:hh + 1]
+    return out
+
+
+def attention_mixer(sd, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch.Tensor:
+    T = h.shape[0]
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    w = lambda n: sd[pre + n].to(F64)
+    q = (h @ w("q").T + w("q.b")).view(T, H, d)
+    k = (h @ w("k").T + w("k.b")).view(T, G, d)
+    v = rms_divide((h @ w("v").T + w("v.b")).view(T, G, dv), eps)
+    gate = torch.sigmoid(h @ w("g").T)                       # [T, H]
+    out = attention_core(q, k, v, gate, m, w("temp"), w("sink"))
     return out.reshape(T, H * dv) @ w("o").T
 
 
@@ -80,12 +89,13 @@ def short_conv_silu(x: torch.Tensor, cw: torch.Tensor) -> torch.Tensor:
     T, C = x.shape
     taps = cw.shape[1]
     y = torch.zeros_like(x)
-    for back in range(taps):
+    for back in range(min(taps, T)):
         y[back:] += x[:T - back] * cw[:, taps - 1 - back]
     return y * torch.sigmoid(y)
 
 
-def delta_mixer(sd, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch.Tensor:
+def delta_inputs(sd, pre: str, m: dict, h: torch.Tensor):
+    """What enters the recurrence: q, k [T, G, d] (unit length, q times d^-1/2), v [T, H, dv], beta and decay [T, H]."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     w = lambda n: sd[pre + n].to(F64)
@@ -94,8 +104,15 @@ def delta_mixer(sd, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch.Ten
     v = short_conv_silu(h @ w("v").T, w("v.conv")).view(T, H, dv)
     q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * d ** -0.5
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    beta = torch.sigmoid(h @ w("b").T)                                                    # [T, H]
-    decay = torch.exp(-torch.exp(w("A_log")) * torch.nn.functional.softplus(h @ w("a").T + w("dt_bias")))   # [T, H]
+    beta = torch.sigmoid(h @ w("b").T)
+    decay = torch.exp(-torch.exp(w("A_log")) * torch.nn.functional.softplus(h @ w("a").T + w("dt_bias")))
+    return q, k, v, beta, decay
+
+
+def delta_core(q, k, v, beta, decay) -> torch.Tensor:
+    """The recurrence from a zero state: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  Returns o [T, H, dv]."""
+    T, H, dv = v.shape
+    G, d = q.shape[1], q.shape[2]
     o = torch.zeros(T, H, dv, dtype=F64)
     for hh in range(H):
         g = hh // (H // G)
@@ -105,10 +122,20 @@ def delta_mixer(sd, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch.Ten
             u = beta[t, hh] * (v[t, hh] - S.T @ k[t, g])
             S = S + torch.outer(k[t, g], u)
             o[t, hh] = S.T @ q[t, g]
-    o = rms_divide(o, eps) * w("norm")
-    gate = (h @ w("g").T)
-    gate = (gate * torch.sigmoid(gate)).view(T, H, dv)
-    return (o * gate).reshape(T, H * dv) @ w("o").T
+    return o
+
+
+def gated_head_norm(o, norm_w, gate_logits, eps):
+    """o [T, H, dv] -> o / rms(o) * w * silu(gate) as [T, H * dv]."""
+    T, H, dv = o.shape
+    gate = gate_logits.view(T, H, dv)
+    return (rms_divide(o, eps) * norm_w * gate * torch.sigmoid(gate)).reshape(T, H * dv)
+
+
+def delta_mixer(sd, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch.Tensor:
+    w = lambda n: sd[pre + n].to(F64)
+    o = delta_core(*delta_inputs(sd, pre, m, h))
+    return gated_head_norm(o, w("norm"), h @ w("g").T, eps) @ w("o").T
 
 
 def feed_forward(sd, pre: str, f: dict, h: torch.Tensor) -> torch.Tensor:
