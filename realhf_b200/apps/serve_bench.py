@@ -1,6 +1,6 @@
 """Prefill / decode throughput of a heterogeneous-stack design next to the closest homogeneous model of equal size, and the
-roofline position of its kernels next to the like kernels of that model.  Reached through `bench.py --serve-bench rapodra`
-(the default workload of bench.py is unaffected).
+roofline position of its kernels next to the like kernels of that model.  Reached through `bench.py --serve-bench rapodra` or
+`--serve-bench tizodra` (the default workload of bench.py is unaffected).
 
 Both models run through `models.generation`: prefill = `prefill_into_state` (the packed prefill `generate` performs) into a
 standing decode state, decode = the CUDA-graph loop of `generate` with the sampler in the graph; random weights, bf16.  Timing: CUDA events, >= 3 warm-up calls, weights + state far larger than L2 per call for
@@ -35,13 +35,32 @@ def rapodra_config(s: dict, n_layers: int = 4) -> dict:
                 vocab=s["vocab"], width=s["width"])
 
 
-def _models(s: dict, n_layers: int, dev):
+TIZODRA_SIZES = {
+    # name: width, query heads, kv heads, qk dim, v dim, window, kept first tokens, conv taps, ff, vocab
+    "1b-like": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=512, keep=64, conv=4, ff=8192, vocab=32000),
+    "7b-like": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=64, conv=4, ff=11008, vocab=32000),
+}
+
+
+def tizodra_config(s: dict, n_layers: int = 4) -> dict:
+    """Delta blocks outside, window-attention blocks inside a loop of one pass (so the re-injection projection is on the path)."""
+    att = dict(type="attention", mixer=dict(dim=s["dim"], heads=s["heads"], kv_heads=s["kv_heads"], vdim=s["vdim"], scale=s["dim"] ** -0.5,
+                                            mask=dict(size=s["window"], keep_first=s["keep"])), mlp=dict(kind="dense", ff=s["ff"]))
+    dlt = dict(type="delta", mixer=dict(conv=s["conv"], dim=s["dim"], heads=s["heads"], kv_heads=s["kv_heads"], vdim=s["vdim"]),
+               mlp=dict(kind="dense", ff=s["ff"]))
+    layers = [dlt if i in (0, n_layers - 1) else att for i in range(n_layers)]
+    return dict(architecture="Tizodra", layers=layers, logit_scale=0.5, loop=dict(start=1, stop=max(2, n_layers - 1), times=1),
+                norm=dict(eps=1e-5), vocab=s["vocab"], width=s["width"])
+
+
+def _models(s: dict, n_layers: int, dev, design: str = "rapodra"):
     from realhf_b200.api.model import ReaLModelConfig
     from realhf_b200.models import hf_io
     from realhf_b200.models.real_model import ReaLModel
-    rc = hf_io.family("rapodra").config_from_dict(rapodra_config(s, n_layers), False)
+    cfg = rapodra_config(s, n_layers) if design == "rapodra" else tizodra_config(s, n_layers)
+    rc = hf_io.family(design).config_from_dict(cfg, False)
     new = ReaLModel(rc, dtype=torch.bfloat16, device=dev).init_random_fast()
-    lc = ReaLModelConfig(n_layers=n_layers, n_kv_heads=s["heads"], n_q_heads=s["heads"], hidden_dim=s["width"], intermediate_dim=s["ff"],
+    lc = ReaLModelConfig(n_layers=n_layers, n_kv_heads=s.get("kv_heads", s["heads"]), n_q_heads=s["heads"], hidden_dim=s["width"], intermediate_dim=s["ff"],
                          vocab_size=s["vocab"], head_dim=s["dim"], n_positions=8192, embd_pdrop=0.0, resid_pdrop=0.0, attn_pdrop=0.0,
                          activation_function="silu", scale_attn_by_inverse_layer_idx=False, use_attention_bias=False,
                          use_attn_proj_bias=False, use_mlp_bias=False, layer_norm_type="rms", mlp_type="llama", apply_rotary=True)
@@ -70,16 +89,16 @@ def _time(fn: Callable[[], None], iters: int, warmup: int = 3, flush: torch.Tens
     return tot / iters
 
 
-def model_numbers(name: str, s: dict, n_layers: int, batch: int, prompt_len: int, new_tokens: int, dev) -> List[dict]:
+def model_numbers(name: str, s: dict, n_layers: int, batch: int, prompt_len: int, new_tokens: int, dev, design: str = "rapodra") -> List[dict]:
     from realhf_b200.api.model import GenerationHyperparameters
     from realhf_b200.models import generation as gen
     os.environ["REAL_GEN_TIMING"] = "1"
     out = []
-    new, old = _models(s, n_layers, dev)
+    new, old = _models(s, n_layers, dev, design)
     g = GenerationHyperparameters(max_new_tokens=new_tokens, min_new_tokens=new_tokens, greedy=True, use_cuda_graph=True)
     ids = torch.randint(3, s["vocab"], (batch * prompt_len,), device=dev)
     cu = torch.arange(0, batch + 1, device=dev, dtype=torch.int32) * prompt_len
-    for label, m in (("rapodra", new), ("llama-equal-size", old)):
+    for label, m in ((design, new), ("llama-equal-size", old)):
         # prefill: the packed prefill into a standing decode state (`prefill_into_state`, what `generate` calls), so that the
         # number is the model's and not the caching allocator's (a fresh multi-GB state per `generate` call can fall into
         # cudaMalloc inside the timed region); decode: the CUDA-graph loop of `generate`
@@ -180,8 +199,118 @@ def kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx: int, de
     return rows
 
 
+def tizodra_kernel_numbers(name: str, s: dict, batch: int, prompt_len: int, ctx: int, dev, peaks: Dict[str, float]) -> List[dict]:
+    """The Tizodra kernels next to the like kernels of the LLaMA path (same token count, heads and head sizes).  Attention FLOPs
+    count the visible (query, key) pairs only; the delta rule has no like kernel: its floor is the fp32 FMA work (the design keeps
+    the recurrence in fp32, so the bf16 tensor-core figure is not its roofline) or its bytes, whichever is slower."""
+    from realhf_b200.api.model import DeltaRuleConfig, WindowAttentionConfig
+    from realhf_b200.models.hetero_block import packed_meta
+    from realhf_b200.ops import attention as A
+    from realhf_b200.ops import functional as OF
+    from realhf_b200.ops import recurrent as RC
+    bf = torch.bfloat16
+    W, H, G, d, dv, win, keep, taps, FF = s["width"], s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"], s["keep"], s["conv"], s["ff"]
+    T = batch * prompt_len
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fp32_tflops = 148 * 128 * 2 * 1.9e9 / 1e12          # 148 SMs x 128 fp32 lanes x 2 flop x ~1.9 GHz
+    rows = []
+
+    def add(kernel, like, ms, nbytes, flops, simt_fp32=False):
+        peak = fp32_tflops if simt_fp32 else peaks["bf16_tflops"]
+        floor_ms = max(nbytes / (peaks["hbm_gbs"] * 1e9), flops / (peak * 1e12)) * 1e3
+        rows.append(dict(bench="kernel", size=name, kernel=kernel, like=like, ms=round(ms, 4), gbytes=round(nbytes / 1e9, 4),
+                         gflop=round(flops / 1e9, 2), roofline_ms=round(floor_ms, 4), frac_of_measured_roofline=round(floor_ms / ms, 4),
+                         flop_peak="fp32 CUDA cores (nominal)" if simt_fp32 else "bf16 tensor (measured)"))
+
+    cu = torch.arange(0, batch + 1, device=dev, dtype=torch.int32) * prompt_len
+    meta = packed_meta(cu, T, torch.arange(batch, dtype=torch.int32, device=dev), None, prompt_len)
+    x32 = torch.randn(T, W, device=dev)
+    xb = x32.to(bf)
+    w = torch.ones(W, device=dev, dtype=bf)
+    # ---- row-wise
+    wte = torch.randn(s["vocab"], W, device=dev).to(bf)
+    ids = torch.randint(0, s["vocab"], (T,), device=dev)
+    add("embed_sinusoid (prefill)", False, _time(lambda: OF.embed_sinusoid(ids, wte, meta.pos), 10, flush=flush), T * W * 6, 0)
+    add("embedding lookup (llama, prefill)", True, _time(lambda: torch.nn.functional.embedding(ids, wte), 10, flush=flush), T * W * 4, 0)
+    add("sublayer_input (RMSNorm of the fp32 stream, prefill)", False, _time(lambda: OF.sublayer_input(x32, w, 1, 1e-5, None, None, bf), 10, flush=flush),
+        T * W * 6, 0)
+    add("residual_add_norm_ (fp32 stream += branch, prefill)", False, _time(lambda: OF.residual_add_norm_(x32, xb, None, 1, 1e-5), 10, flush=flush),
+        T * W * 10, 0)
+    add("add_rmsnorm (llama, prefill)", True, _time(lambda: OF.add_rmsnorm(xb, xb, w, 1e-5), 10, flush=flush), T * W * 8, 0)
+    up = torch.randn(T, FF, device=dev).to(bf)
+    add("relu2 (prefill)", False, _time(lambda: OF.relu2(up), 10, flush=flush), T * FF * 4, 0)
+    gu = torch.randn(T, 2 * FF, device=dev).to(bf)
+    add("gated_act silu (llama, prefill)", True, _time(lambda: OF.gated_act(gu, "silu"), 10, flush=flush), T * FF * 6, 0)
+    # ---- window attention
+    a = WindowAttentionConfig(n_heads=H, n_kv_heads=G, qk_dim=d, v_dim=dv, scale=d ** -0.5, window=win, keep_first=keep)
+    ld = H * d + G * (d + dv) + (H + 7) // 8 * 8
+    qkvg = torch.randn(T, ld, device=dev).to(bf)
+    temp = torch.ones(H, device=dev, dtype=bf)
+    sink = torch.zeros(H, device=dev, dtype=bf)
+    S = prompt_len + 64
+    rows_c = a.cache_rows(S)
+    kc = torch.zeros(batch, G, rows_c, d, device=dev, dtype=bf)
+    vc = torch.zeros(batch, G, rows_c, dv, device=dev, dtype=bf)
+    add("value_norm_store (prefill: value norm + cache fill)", False,
+        _time(lambda: A.value_norm_store(qkvg, a, 1e-5, kc, vc, meta.tok_slot, meta.pos, meta.remain), 10, flush=flush),
+        T * G * (d + 3 * dv) * 2, 0)
+    v_n = A.value_norm_store(qkvg, a, 1e-5, None, None, meta.tok_slot, meta.pos, meta.remain)
+    pairs = batch * sum(min(p + 1, win) + max(0, min(keep, p + 1 - win)) for p in range(prompt_len))
+    add("sink_window_attention (prefill)", False,
+        _time(lambda: A.sink_window_attention(qkvg, v_n, a, temp, sink, meta.pos, cu, prompt_len), 3, warmup=1, flush=flush),
+        T * (H * (d + dv) + G * (d + dv)) * 2, 2.0 * pairs * H * (d + dv))
+    qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    full_pairs = batch * prompt_len * (prompt_len + 1) // 2
+    add("varlen attention tcgen05 (llama, prefill, full causal)", True,
+        _time(lambda: A.varlen_attention_qkv(qkv, cu, prompt_len, H, G, d, None, True), 5, flush=flush), T * (2 * H + 2 * G) * d * 2,
+        4.0 * full_pairs * H * d)
+    keys = min(ctx + 1, win) + max(0, min(keep, ctx + 1 - win))
+    rows_d = a.cache_rows(ctx + 64)
+    kc = torch.randn(batch, G, rows_d, d, device=dev).to(bf)
+    vc = torch.randn(batch, G, rows_d, dv, device=dev).to(bf)
+    lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+    q1 = torch.randn(batch, ld, device=dev).to(bf)
+    add(f"sink_window_decode_attention (ctx {ctx}, {keys} keys)", False,
+        _time(lambda: A.sink_window_decode_attention(q1, a, temp, sink, kc, vc, lens, None, 1e-5), 10, flush=flush),
+        batch * keys * G * (d + dv) * 2, 2.0 * batch * H * keys * (d + dv))
+    kl = torch.zeros(batch, G, ctx + 64, d, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    vl = torch.zeros(batch, G, ctx + 64, d, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    qkv1 = torch.randn(batch, (H + 2 * G) * d, device=dev).to(bf)
+    cos, sin = OF.rope_tables(ctx + 64, d, 10000.0, dev)
+    add(f"decode_attention (llama, ctx {ctx}, all {ctx + 1} keys)", True,
+        _time(lambda: A.decode_attention(qkv1, kl, vl, lens, H, G, d, None, cos, sin), 10, flush=flush),
+        batch * (ctx + 1) * G * d * 2 * 2, 4.0 * batch * H * (ctx + 1) * d)
+    # ---- delta rule
+    dl = DeltaRuleConfig(n_heads=H, n_kv_heads=G, qk_dim=d, v_dim=dv, conv_taps=taps)
+    C = dl.conv_channels
+    ldp = C + H * dv + (2 * H + 7) // 8 * 8
+    proj = torch.randn(T, ldp, device=dev).to(bf)
+    conv_w = (torch.randn(C, taps, device=dev) * 0.5).to(bf)
+    A_log = torch.zeros(H, device=dev, dtype=bf)
+    dtb = torch.zeros(H, device=dev, dtype=bf)
+    conv_state = torch.zeros(batch, taps - 1, C, device=dev)
+    s_state = torch.zeros(batch, H, d, dv, device=dev)
+    add("delta_prepare (prefill: conv + SiLU + unit norms + gates)", False,
+        _time(lambda: RC.delta_prepare(proj, conv_w, A_log, dtb, dl, meta.pos, conv_state, meta.tok_slot, meta.remain), 10, flush=flush),
+        T * (C + 2 * H) * (2 + 4), T * C * 2.0 * taps, simt_fp32=True)
+    u = RC.delta_prepare(proj, conv_w, A_log, dtb, dl, meta.pos, conv_state, meta.tok_slot, meta.remain)
+    add("delta_rule_scan (prefill, fp32 recurrence)", False,
+        _time(lambda: RC.delta_rule_scan(u, dl, cu, s_state, meta.seq_slot), 3, warmup=1, flush=flush),
+        T * (C + 2 * H + H * dv) * 4, T * H * 8.0 * d * dv, simt_fp32=True)
+    o = RC.delta_rule_scan(u, dl, cu, s_state, meta.seq_slot)
+    add("gated_head_norm (prefill)", False, _time(lambda: RC.gated_head_norm(o, torch.ones(dv, device=dev, dtype=bf), proj[:, C:C + H * dv], 1e-5, bf),
+                                                  10, flush=flush), T * H * dv * 8, 0)
+    p1 = torch.randn(batch, ldp, device=dev).to(bf)
+    add("delta_prepare_step (decode)", False, _time(lambda: RC.delta_prepare_step(p1, conv_w, A_log, dtb, dl, conv_state, None), 10, flush=flush),
+        batch * (C * (2 + 4 + 8 * (taps - 1)) + C * taps * 2 / batch), 0)
+    u1 = RC.delta_prepare_step(p1, conv_w, A_log, dtb, dl, conv_state, None)
+    add("delta_rule_step (decode: state read + write)", False, _time(lambda: RC.delta_rule_step(u1, dl, s_state, None), 10, flush=flush),
+        batch * H * d * dv * 8, batch * H * 8.0 * d * dv, simt_fp32=True)
+    return rows
+
+
 def run(design: str, sizes: List[str] = None, n_layers: int = 4) -> List[dict]:
-    assert design == "rapodra"
+    assert design in ("rapodra", "tizodra")
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     peaks = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
@@ -192,10 +321,12 @@ def run(design: str, sizes: List[str] = None, n_layers: int = 4) -> List[dict]:
         if "hbm_gbs" in d and "bf16_tflops" in d:
             peaks = dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), source="measured")
     results = [dict(bench="peaks", **peaks)]
-    for name in sizes or list(SIZES):
-        s = SIZES[name]
-        results += model_numbers(name, s, n_layers, batch=32, prompt_len=1024, new_tokens=33, dev=dev)
-        results += kernel_numbers(name, s, batch=32, prompt_len=1024, ctx=2048, dev=dev, peaks=peaks)
+    table = SIZES if design == "rapodra" else TIZODRA_SIZES
+    for name in sizes or list(table):
+        s = table[name]
+        results += model_numbers(name, s, n_layers, batch=32, prompt_len=1024, new_tokens=33, dev=dev, design=design)
+        kn = kernel_numbers if design == "rapodra" else tizodra_kernel_numbers
+        results += kn(name, s, batch=32, prompt_len=1024, ctx=2048, dev=dev, peaks=peaks)
     for r in results:
         print(json.dumps(r), flush=True)
     return results

@@ -430,6 +430,14 @@ def sink_window_attention_ref(qkvg, v_n, a, temp, sink, cu_seqlens):
     return out.reshape(T, H * dv).to(qkvg.dtype)
 
 
+def _sink_tc_ok(qkvg, v_n, a) -> bool:
+    """The tcgen05 form takes 16-bit operands with equal query / value head size of 64 or 128 (softmax statistics in fp32, the
+    weights rounded to the operand type for the P.V product); `REAL_WINDOW_ATTN=simt` selects the all-fp32 CUDA-core kernel."""
+    return (os.environ.get("REAL_WINDOW_ATTN", "tcgen05") == "tcgen05" and qkvg.dtype in (torch.bfloat16, torch.float16)
+            and a.qk_dim == a.v_dim and a.qk_dim in (64, 128) and qkvg.stride(0) % 8 == 0 and qkvg.data_ptr() % 16 == 0
+            and (a.n_heads * a.qk_dim) % 8 == 0 and v_n.data_ptr() % 16 == 0)
+
+
 def sink_window_attention(qkvg, v_n, a, temp, sink, pos, cu_seqlens, max_seqlen=None):
     """Packed causal attention of a window-attention block over the batch's own keys (every sequence starts at position 0):
     softmax_j(q_i . k_j * scale * temp_h - slope_h (i - j)) with the sink logit in the denominator, over j <= i with
@@ -439,6 +447,11 @@ def sink_window_attention(qkvg, v_n, a, temp, sink, pos, cu_seqlens, max_seqlen=
         out = torch.empty(T, a.n_heads * a.v_dim, dtype=qkvg.dtype, device=qkvg.device)
         if max_seqlen is None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        if _sink_tc_ok(qkvg, v_n, a):
+            lib().sink_window_attention_tc(qkvg, v_n, out, temp, sink, cu_seqlens, max_seqlen, a.n_heads, a.n_kv_heads, a.qk_dim, a.scale,
+                                           a.window if a.window is not None else -1, a.keep_first,
+                                           a.slope_base if a.slope_base is not None else -1.0, bool(a.out_gate))
+            return out
         lib().sink_window_attention(qkvg, v_n, out, temp, sink, cu_seqlens, max_seqlen, a.n_heads, a.n_kv_heads, a.qk_dim, a.v_dim, a.scale,
                                     a.window if a.window is not None else -1, a.keep_first,
                                     a.slope_base if a.slope_base is not None else -1.0, bool(a.out_gate))

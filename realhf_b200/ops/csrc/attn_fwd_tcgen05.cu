@@ -25,6 +25,12 @@
 // the MN-major B operand (keys are the K dimension, head-dim contiguous), exactly the wgrad operand form of the GEMM.
 //
 // Outputs: O [T, nq, D] and LSE [nq, T] (natural log, scale applied) in the layout flash-attn's backward consumes.
+//
+// kSink variant (`WindowAttentionConfig`, inference only, no LSE): score = s * scale * temp_h - slope_h * (i - j) with
+// slope_h = 2^(-slope_base (h + 1) / nq) (formed per element in the log2 domain with one extra FMA in each pass), a sliding
+// window that also keeps the first `keep` keys (the key tiles of [0, keep) that lie below the window's first tile are walked
+// first by all three roles), a per-head sink logit that starts the running maximum with denominator 1, and the row's output
+// times sigmoid(gate logit of its head).
 #include "gemm_common.cuh"
 
 namespace {
@@ -42,6 +48,13 @@ struct AttnParams {
   float scale;
   int causal;
   int window;             // > 0 (with causal): a query at position i sees keys (i - window, i]
+  // kSink variant only
+  int keep;               // with a window: keys [0, keep) stay visible to every later query
+  const void* temp;       // [nq] per-head factor on the scaled score, or null
+  const void* sink;       // [nq] per-head sink logit, or null
+  const void* gate;       // gate logits, element (t, h) at gate[t * gate_ld + h], or null
+  int64_t gate_ld;
+  float slope_base;       // < 0: no distance term
 };
 
 template <int kD> struct ACfg {
@@ -68,7 +81,7 @@ template <> RB_DEVICE uint32_t pack2<__half>(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int kD, typename T, int kFmt>
+template <int kD, typename T, int kFmt, bool kSink = false>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q,
                                                                    const __grid_constant__ CUtensorMap tma_k,
                                                                    const __grid_constant__ CUtensorMap tma_v, AttnParams p) {
@@ -83,7 +96,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   const int kv_len = p.causal ? min(L, q0 + kBQ) : L;
   const int win = (p.causal && p.window > 0) ? p.window : 0;
   const int tile0 = win > 0 ? max(0, q0 - win + 1) / kBKV : 0;   // first key tile any row of this CTA can see
-  const int n_kv = RB_CEIL_DIV(kv_len, kBKV) - tile0;             // >= 1: the diagonal tile is always visible
+  // kSink: the tiles of the kept first keys that lie wholly below tile0 come first in every role's walk
+  const int n_keep = (kSink && win > 0) ? min(RB_CEIL_DIV(p.keep, kBKV), tile0) : 0;
+  const int n_kv = n_keep + RB_CEIL_DIV(kv_len, kBKV) - tile0;    // >= 1: the diagonal tile is always visible
+  auto tile_of = [&](int j) { return j < n_keep ? j : tile0 + j - n_keep; };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -125,7 +141,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t par = (uint32_t)(j >> 1) & 1u;
-        const int row = tok0 + (tile0 + j) * kBKV;
+        const int row = tok0 + tile_of(j) * kBKV;
         ptx::mbar_wait(bar(K_EMPTY + st), par ^ 1);
         ptx::mbar_arrive_expect_tx(bar(K_FULL + st), C::kKVBytes);
 #pragma unroll
@@ -197,6 +213,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     const uint32_t p_row = sP + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
     const uint32_t sw = (uint32_t)(row & 7);
     float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+    // kSink: scores live in the log2 domain, t = s * c2 - slope2 * (q_pos - key_pos); the sink starts the maximum
+    float c2 = 0.f, slope2 = 0.f;
+    if constexpr (kSink) {
+      c2 = sl2 * (p.temp ? rb::to_f(reinterpret_cast<const T*>(p.temp)[head]) : 1.f);
+      slope2 = p.slope_base >= 0.f ? exp2f(-p.slope_base * (float)(head + 1) / (float)p.nq) * 1.4426950408889634f : 0.f;
+      if (p.sink) { m_run = rb::to_f(reinterpret_cast<const T*>(p.sink)[head]) * 1.4426950408889634f; l_run = 1.f; }
+    }
     float O[kD];
 #pragma unroll
     for (int i = 0; i < kD; ++i) O[i] = 0.f;
@@ -220,7 +243,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 
     for (int j = 0; j < n_kv; ++j) {
       const int b = j & 1;
-      const int kv0 = (tile0 + j) * kBKV;
+      const int kv0 = tile_of(j) * kBKV;
       ptx::mbar_wait(bar(S_FULL + b), (uint32_t)(j >> 1) & 1u);
       ptx::tc_fence_after();
       // only the last tile of the sequence, the diagonal tile and the tiles the window's lower edge crosses need per-element
@@ -228,6 +251,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const bool need_mask = (kv0 + kBKV > L) || (p.causal && kv0 + kBKV - 1 > q0) || (win > 0 && q0 + kBQ - win > kv0);
       const int lim = (p.causal ? min(L, q_pos + 1) : L) - kv0;  // local key columns [lo, lim) are visible to this row
       const int lo = win > 0 ? q_pos - win + 1 - kv0 : 0;
+      const int kept = kSink ? p.keep - kv0 : 0;                 // kSink: local columns below `kept` stay visible under `lo`
+      auto hidden = [&](int col) { return col >= lim || (col < lo && (!kSink || col >= kept)); };
+      const float base = kSink ? slope2 * (float)(kv0 - q_pos) : 0.f;
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < kBKV / 32; ++c) {
@@ -237,14 +263,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float s = __uint_as_float(r[i]);
-          if (need_mask && (c * 32 + i >= lim || c * 32 + i < lo)) s = -INFINITY;
+          if constexpr (kSink) s = fmaf(s, c2, fmaf(slope2, (float)(c * 32 + i), base));
+          if (need_mask && hidden(c * 32 + i)) s = -INFINITY;
           mx = fmaxf(mx, s);
         }
       }
       const float m_new = fmaxf(m_run, mx);
       const float m_eff = (m_new == -INFINITY) ? 0.f : m_new;  // fully masked so far: keep exp2 arguments finite
-      const float alpha = exp2f((m_run - m_eff) * sl2);
-      const float neg_m = -m_eff * sl2;
+      const float alpha = kSink ? exp2f(m_run - m_eff) : exp2f((m_run - m_eff) * sl2);
+      const float neg_m = kSink ? -m_eff : -m_eff * sl2;
       if (j > 0) ptx::mbar_wait(bar(P_EMPTY), (uint32_t)(j - 1) & 1u);  // PV_{j-1} finished reading the P buffer
       float sum = 0.f;
 #pragma unroll
@@ -255,11 +282,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, neg_m));
-          float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, neg_m));
+          float e0, e1;
+          if constexpr (kSink) {
+            e0 = exp2f(fmaf(__uint_as_float(r[i]), c2, fmaf(slope2, (float)(c * 32 + i), base)) + neg_m);
+            e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), c2, fmaf(slope2, (float)(c * 32 + i + 1), base)) + neg_m);
+          } else {
+            e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, neg_m));
+            e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, neg_m));
+          }
           if (need_mask) {
-            if (c * 32 + i >= lim || c * 32 + i < lo) e0 = 0.f;
-            if (c * 32 + i + 1 >= lim || c * 32 + i + 1 < lo) e1 = 0.f;
+            if (hidden(c * 32 + i)) e0 = 0.f;
+            if (hidden(c * 32 + i + 1)) e1 = 0.f;
           }
           sum += e0 + e1;
           w[i >> 1] = pack2<T>(e0, e1);
@@ -286,7 +319,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     fold(n_kv - 1, alpha_prev);
 
     if (q_pos < L) {
-      const float inv = 1.f / l_run;
+      float inv = 1.f / l_run;
+      if constexpr (kSink) {
+        if (p.gate) inv *= 1.f / (1.f + __expf(-rb::to_f(reinterpret_cast<const T*>(p.gate)[(int64_t)(tok0 + q_pos) * p.gate_ld + head])));
+      }
       T* dst = reinterpret_cast<T*>(p.out) + (int64_t)(tok0 + q_pos) * p.out_ld + (int64_t)head * kD;
 #pragma unroll
       for (int i = 0; i < kD; i += 8) {
@@ -297,7 +333,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         v.w = pack2<T>(O[i + 6] * inv, O[i + 7] * inv);
         *reinterpret_cast<uint4*>(dst + i) = v;
       }
-      p.lse[(int64_t)head * p.T + tok0 + q_pos] = m_run * p.scale + __logf(l_run);
+      if constexpr (!kSink) p.lse[(int64_t)head * p.T + tok0 + q_pos] = m_run * p.scale + __logf(l_run);
     }
   }
 
@@ -309,11 +345,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   }
 }
 
-template <int kD, typename T, int kFmt>
+template <int kD, typename T, int kFmt, bool kSink = false>
 int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int B,
                     int max_seqlen, cudaStream_t s) {
   using C = ACfg<kD>;
-  auto kern = attn_fwd_kernel<kD, T, kFmt>;
+  auto kern = attn_fwd_kernel<kD, T, kFmt, kSink>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) return -30;
@@ -344,7 +380,7 @@ extern "C" int rb_attn_fwd_window(const void* q, const void* k, const void* v, v
   if (!make_tmap(&mk, k, bf, T, (uint64_t)nkv * hd, k_ld, 64, kBKV)) return -11;
   if (!make_tmap(&mv, v, bf, T, (uint64_t)nkv * hd, v_ld, 64, 64)) return -12;  // 64-key halves, see the producer
   if (window > 0 && !causal) return -6;
-  AttnParams p{cu_seqlens, out, lse, out_ld, T, nq, nkv, scale, causal, window};
+  AttnParams p{cu_seqlens, out, lse, out_ld, T, nq, nkv, scale, causal, window, 0, nullptr, nullptr, nullptr, 0, -1.f};
   if (hd == 128) {
     return bf ? launch_attn_fwd<128, __nv_bfloat16, 1>(mq, mk, mv, p, B, max_seqlen, s)
               : launch_attn_fwd<128, __half, 0>(mq, mk, mv, p, B, max_seqlen, s);
@@ -357,4 +393,31 @@ extern "C" int rb_attn_fwd(const void* q, const void* k, const void* v, void* ou
                            int64_t q_ld, int64_t k_ld, int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd,
                            int max_seqlen, float scale, int causal, int dt, cudaStream_t s) {
   return rb_attn_fwd_window(q, k, v, out, lse, cu_seqlens, q_ld, k_ld, v_ld, out_ld, T, B, nq, nkv, hd, max_seqlen, scale, causal, 0, dt, s);
+}
+
+// Window attention with a sink on the tensor cores (see the kSink notes at the top): q / k / v as for rb_attn_fwd (equal query /
+// value head size of 64 or 128), temp / sink [nq] in the operand type or null, gate logits at gate[t * gate_ld + h] or null,
+// window <= 0 = every earlier key, keep = first keys that stay visible, slope_base < 0 = no distance term.
+extern "C" int rb_attn_fwd_sink(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens, int64_t q_ld, int64_t k_ld,
+                                int64_t v_ld, int64_t out_ld, int T, int B, int nq, int nkv, int hd, int max_seqlen, float scale, int window,
+                                int keep, const void* temp, const void* sink, const void* gate, int64_t gate_ld, float slope_base, int dt,
+                                cudaStream_t s) {
+  if (hd != 128 && hd != 64) return -1;
+  if (dt != 1 && dt != 2) return -2;
+  if (nq % nkv != 0 || T <= 0 || B <= 0 || max_seqlen <= 0) return -3;
+  if ((q_ld | k_ld | v_ld | out_ld) % 8 != 0) return -4;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return -5;
+  CUtensorMap mq, mk, mv;
+  const int bf = dt == 1;
+  if (!make_tmap(&mq, q, bf, T, (uint64_t)nq * hd, q_ld, 64, kBQ)) return -10;
+  if (!make_tmap(&mk, k, bf, T, (uint64_t)nkv * hd, k_ld, 64, kBKV)) return -11;
+  if (!make_tmap(&mv, v, bf, T, (uint64_t)nkv * hd, v_ld, 64, 64)) return -12;
+  AttnParams p{cu_seqlens, out, nullptr, out_ld, T, nq, nkv, scale, 1, window > 0 ? window : 0, window > 0 ? keep : 0, temp, sink, gate, gate_ld,
+               slope_base};
+  if (hd == 128) {
+    return bf ? launch_attn_fwd<128, __nv_bfloat16, 1, true>(mq, mk, mv, p, B, max_seqlen, s)
+              : launch_attn_fwd<128, __half, 0, true>(mq, mk, mv, p, B, max_seqlen, s);
+  }
+  return bf ? launch_attn_fwd<64, __nv_bfloat16, 1, true>(mq, mk, mv, p, B, max_seqlen, s)
+            : launch_attn_fwd<64, __half, 0, true>(mq, mk, mv, p, B, max_seqlen, s);
 }

@@ -172,6 +172,26 @@ def test_window_attention_packed(device, dtype, H, G, d, dv, window, keep):
     assert got.dtype == dtype and close(got, want, dtype, 2e-5, 0.03)
 
 
+@pytest.mark.parametrize("device,dtype", [CPU, GPU16])
+@pytest.mark.parametrize("H,G,d,window,keep", [(2, 1, 64, 100, 5), (1, 1, 128, 128, 0), (2, 2, 64, 129, 130), (4, 2, 64, 400, 300), (2, 1, 128, None, 0),
+                                               (2, 2, 64, 1, 1), (2, 1, 128, 260, 129)])
+def test_window_attention_tensor_core_shapes(device, dtype, H, G, d, window, keep, monkeypatch):
+    """Head shapes the tensor-core kernel takes, windows and kept ranges below / at / above its 128-key tiles, sequences that end
+    inside a tile; the all-fp32 kernel on the same input agrees."""
+    lens = [600, 1, 127, 128, 129, 385]
+    a, m, qkvg, temp, sink = attn_case(H, G, d, d, window, keep, H + d, dtype, lens)
+    want = attn_oracle(a, m, qkvg, temp, sink, lens)
+    meta = pack_meta(lens, device)
+    v_n = A.value_norm_store(qkvg.to(device), a, 1e-5, None, None, meta.tok_slot, meta.pos, meta.remain)
+    got = A.sink_window_attention(qkvg.to(device), v_n, a, temp.to(device), sink.to(device), meta.pos, meta.cu_seqlens, max(lens))
+    assert close(got, want, dtype, 2e-5, 0.03)
+    if device == "cuda":
+        assert A._sink_tc_ok(qkvg.to(device), v_n, a)
+        monkeypatch.setenv("REAL_WINDOW_ATTN", "simt")
+        other = A.sink_window_attention(qkvg.to(device), v_n, a, temp.to(device), sink.to(device), meta.pos, meta.cu_seqlens, max(lens))
+        assert close(other, want, dtype, 2e-5, 0.03) and close(got, other.double().cpu(), dtype, 2e-5, 0.03)
+
+
 @pytest.mark.parametrize("device,dtype", ALL)
 @pytest.mark.parametrize("H,G,d,dv,window,keep", ATTN_SHAPES)
 def test_window_attention_prefill_cache_then_decode(device, dtype, H, G, d, dv, window, keep):
