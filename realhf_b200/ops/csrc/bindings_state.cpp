@@ -46,6 +46,8 @@ int rb_sink_window_prefill(const void*, int64_t, const void*, void*, const void*
                            int, float, int, int, cudaStream_t);
 int rb_sink_window_decode(const void*, int64_t, void*, const void*, const void*, void*, void*, const int*, const int*, int, int, int, int, int, int,
                           float, int, int, float, int, int, float, int, cudaStream_t);
+int rb_sink_window_decode_fast(const void*, int64_t, void*, const void*, const void*, void*, void*, const int*, const int*, float*, float*, int, int,
+                               int, int, int, int, float, int, int, float, int, int, float, int, cudaStream_t);
 int rb_attn_fwd_sink(const void*, const void*, const void*, void*, const int*, int64_t, int64_t, int64_t, int64_t, int, int, int, int, int, int, float,
                      int, int, const void*, const void*, const void*, int64_t, float, int, cudaStream_t);
 int rb_delta_prepare(const void*, int64_t, int, const void*, const void*, const void*, float*, const int*, float*, const int*, const int*, const int*,
@@ -143,6 +145,26 @@ void sink_window_decode_attention(const Tensor& qkvg, Tensor out, const OptT& te
   TORCH_CHECK(kc.scalar_type() == qkvg.scalar_type() && vc.scalar_type() == qkvg.scalar_type() && out.scalar_type() == qkvg.scalar_type());
   TORCH_CHECK(slots.has_value() || kc.size(0) >= B);
   c10::cuda::CUDAGuard g(qkvg.device());
+  const int rep = (int)(H / G);
+  if (qkvg.scalar_type() != at::kFloat && d == dv && (d == 64 || d == 128) && (rep == 1 || rep == 2 || rep == 4 || rep == 8) &&
+      qkvg.stride(0) % 8 == 0 && (H * d) % 8 == 0 && reinterpret_cast<uintptr_t>(qkvg.data_ptr()) % 16 == 0) {
+    // enough CTAs for two per SM, at least 128 keys per split (the cache's row count bounds the visible keys)
+    const int64_t rows = kc.size(2);
+    int splits = (int)std::min<int64_t>(std::max<int64_t>(1, (2 * 148 + B * G - 1) / (B * G)), std::max<int64_t>(1, rows / 128));
+    splits = std::min(splits, 32);
+    Tensor pa, pm;
+    if (splits > 1) {
+      pa = at::empty({B, H, splits, d}, qkvg.options().dtype(at::kFloat));
+      pm = at::empty({B, H, splits, 2}, qkvg.options().dtype(at::kFloat));
+    }
+    const int rcf = rb_sink_window_decode_fast(qkvg.data_ptr(), qkvg.stride(0), out.data_ptr(), same_type_ptr(temp, qkvg, H, "temp"),
+                                               same_type_ptr(sink, qkvg, H, "sink"), kc.data_ptr(), vc.data_ptr(), lens.data_ptr<int>(),
+                                               int_ptr(slots, B, "slots"), splits > 1 ? pa.data_ptr<float>() : nullptr,
+                                               splits > 1 ? pm.data_ptr<float>() : nullptr, splits, (int)B, (int)H, (int)G, (int)d, (int)rows, (float)scale,
+                                               (int)window, (int)keep, (float)slope_base, gate ? 1 : 0, do_norm ? 1 : 0, (float)eps, dt_code(qkvg),
+                                               cur_stream());
+    if (rcf == 0) return;
+  }
   const int rc = rb_sink_window_decode(qkvg.data_ptr(), qkvg.stride(0), out.data_ptr(), same_type_ptr(temp, qkvg, H, "temp"),
                                        same_type_ptr(sink, qkvg, H, "sink"), kc.data_ptr(), vc.data_ptr(), lens.data_ptr<int>(), int_ptr(slots, B, "slots"),
                                        (int)B, (int)H, (int)G, (int)d, (int)dv, (int)kc.size(2), (float)scale, (int)window, (int)keep, (float)slope_base,

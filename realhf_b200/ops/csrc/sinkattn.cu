@@ -349,6 +349,232 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
     }
 }
 
+// ------------------------------------------------------------------------------------------------ decode, 16-bit fast path
+// Equal query / value head size HD of 64 or 128, 16-bit storage: the streaming design of the dense-cache decode kernel
+// (attn_decode.cu).  A group of HD / 8 lanes owns one cache row at a time with 16-byte loads, REP query heads share every load,
+// the loop is unrolled x4, and the visible keys are cut into `splits` ranges (grid.z) whose partial (max, sum, acc) are merged
+// by a second kernel, so that a batch of few rows still fills the GPU.  The visible keys are indexed 0 .. nk - 1 (kept first
+// tokens, then the window); index -> cache row needs no division (the ring wraps at most once inside a window).
+constexpr int kFastWarps = 4, kFastThreads = kFastWarps * 32;
+
+template <typename T> RB_DEVICE void f_load8(const T* p, float* f) {
+  rb::Pack<T, 8> v = *reinterpret_cast<const rb::Pack<T, 8>*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = rb::to_f(v.v[i]);
+}
+template <typename T> RB_DEVICE void f_store8(T* p, const float* f) {
+  rb::Pack<T, 8> v;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v.v[i] = rb::from_f<T>(f[i]);
+  *reinterpret_cast<rb::Pack<T, 8>*>(p) = v;
+}
+
+struct FastParams {
+  DecodeParams d;
+  float* part_acc;   // [B, H, splits, HD]
+  float* part_ml;    // [B, H, splits, 2]
+  int splits;
+};
+
+template <typename T, int HD, int REP>
+__global__ void __launch_bounds__(kFastThreads) sink_window_decode_fast_kernel(FastParams fp) {
+  const DecodeParams& p = fp.d;
+  constexpr int LPR = HD / 8, RPW = 32 / LPR;
+  const int b = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane % LPR, rsel = lane / LPR;
+  const int slot = p.slots ? p.slots[b] : b;
+  const int n = p.lens[slot];
+  const T* row_in = reinterpret_cast<const T*>(p.qkvg) + (int64_t)b * p.ld;
+  const int ok = p.H * HD, ov = ok + p.G * HD, og = ov + p.G * HD;
+  T* kc = reinterpret_cast<T*>(p.kc) + ((int64_t)slot * p.G + g) * p.rows * HD;
+  T* vc = reinterpret_cast<T*>(p.vc) + ((int64_t)slot * p.G + g) * p.rows * HD;
+
+  float q[REP][8], slope[REP], kn[8], vn[8];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    const int h = g * REP + r;
+    f_load8(row_in + h * HD + sub * 8, q[r]);
+    const float mul = p.scale * (p.temp ? rb::to_f(reinterpret_cast<const T*>(p.temp)[h]) : 1.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[r][i] *= mul;
+    slope[r] = p.slope_base >= 0.f ? exp2f(-p.slope_base * (float)(h + 1) / (float)p.H) : 0.f;
+  }
+  f_load8(row_in + ok + g * HD + sub * 8, kn);
+  f_load8(row_in + ov + g * HD + sub * 8, vn);
+  if (p.do_norm) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(vn[i], vn[i], ss);
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, LPR);
+    const float rs = 1.f / sqrtf(ss / (float)HD + p.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vn[i] = rb::to_f(rb::from_f<T>(vn[i] * rs));     // as later steps will read it from the cache
+  }
+  const int ring = max(p.rows - p.keep, 1);
+  const int lo = p.window < 0 ? 0 : max(0, n - p.window + 1);
+  const int ka = p.window < 0 ? 0 : min(p.keep, lo);
+  const bool flat = lo < p.keep;                       // every visible position still lives in row = position
+  const int r_lo = flat ? 0 : (lo - p.keep) % ring;
+  auto pos_of = [&](int idx) { return idx < ka ? idx : lo + idx - ka; };
+  auto row_of = [&](int idx) {
+    if (idx < ka) return idx;
+    const int w = idx - ka;
+    if (flat) return lo + w;
+    const int rr = r_lo + w;
+    return p.keep + (rr >= ring ? rr - ring : rr);
+  };
+  const int nk = ka + (n - lo + 1);                    // the last index is the new token itself
+  if (split == 0 && warp == 0 && rsel == 0) {
+    const int64_t rn = row_of(nk - 1);
+    f_store8(kc + rn * HD + sub * 8, kn);
+    f_store8(vc + rn * HD + sub * 8, vn);
+  }
+  const int cached = nk - 1;
+  const int per = RB_CEIL_DIV(cached, fp.splits);
+  const int i0 = min(cached, split * per), i1 = min(cached, i0 + per);
+
+  float m[REP], l[REP], acc[REP][8];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    m[r] = -INFINITY; l[r] = 0.f;
+    if (p.sink && split == 0 && warp == 0 && rsel == 0) { m[r] = rb::to_f(reinterpret_cast<const T*>(p.sink)[g * REP + r]); l[r] = 1.f; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[r][i] = 0.f;
+  }
+  const unsigned gmask = (LPR == 32) ? 0xffffffffu : (((1u << LPR) - 1u) << (rsel * LPR));
+  auto consume = [&](const float* kf, const float* vf, int idx) {
+    const float dist = (float)(n - pos_of(idx));
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s = fmaf(q[r][i], kf[i], s);
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(gmask, s, o, LPR);
+      s -= slope[r] * dist;
+      const float mn = fmaxf(m[r], s);
+      const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mn), pr = expf(s - mn);
+      l[r] = l[r] * corr + pr;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[r][i] = fmaf(acc[r][i], corr, pr * vf[i]);
+      m[r] = mn;
+    }
+  };
+  constexpr int UNROLL = 4;
+  const int step = kFastWarps * RPW;
+  int s0 = i0 + warp * RPW + rsel;
+  for (; s0 + (UNROLL - 1) * step < i1; s0 += UNROLL * step) {
+    float kf[UNROLL][8], vf[UNROLL][8];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t rr = row_of(s0 + u * step);
+      f_load8(kc + rr * HD + sub * 8, kf[u]);
+      f_load8(vc + rr * HD + sub * 8, vf[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) consume(kf[u], vf[u], s0 + u * step);
+  }
+  for (; s0 < i1; s0 += step) {
+    float kf[8], vf[8];
+    const int64_t rr = row_of(s0);
+    f_load8(kc + rr * HD + sub * 8, kf);
+    f_load8(vc + rr * HD + sub * 8, vf);
+    consume(kf, vf, s0);
+  }
+  if (split == fp.splits - 1 && warp == 0 && rsel == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) kn[i] = rb::to_f(rb::from_f<T>(kn[i]));
+    consume(kn, vn, nk - 1);
+  }
+  __syncwarp();
+  __shared__ float sm_acc[kFastWarps][REP][HD];
+  __shared__ float sm_m[kFastWarps][REP], sm_l[kFastWarps][REP];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m[r], o), l2 = __shfl_xor_sync(0xffffffffu, l[r], o);
+      const float mn = fmaxf(m[r], m2);
+      const float c1 = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mn), c2 = (m2 == -INFINITY) ? 0.f : expf(m2 - mn);
+      l[r] = l[r] * c1 + l2 * c2;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a2 = __shfl_xor_sync(0xffffffffu, acc[r][i], o);
+        acc[r][i] = acc[r][i] * c1 + a2 * c2;
+      }
+      m[r] = mn;
+    }
+    if (rsel == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sm_acc[warp][r][sub * 8 + i] = acc[r][i];
+      if (sub == 0) { sm_m[warp][r] = m[r]; sm_l[warp][r] = l[r]; }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < REP * HD; idx += kFastThreads) {
+    const int r = idx / HD, c = idx % HD;
+    float mg = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kFastWarps; ++w) mg = fmaxf(mg, sm_m[w][r]);
+    float lg = 0.f, ag = 0.f;
+#pragma unroll
+    for (int w = 0; w < kFastWarps; ++w) {
+      const float cf = (sm_m[w][r] == -INFINITY) ? 0.f : expf(sm_m[w][r] - mg);
+      lg += sm_l[w][r] * cf;
+      ag += sm_acc[w][r][c] * cf;
+    }
+    const int h = g * REP + r;
+    if (fp.splits == 1) {
+      float f = lg > 0.f ? 1.f / lg : 0.f;
+      if (p.gate) f *= 1.f / (1.f + expf(-rb::to_f(row_in[og + h])));
+      reinterpret_cast<T*>(p.out)[(int64_t)b * p.H * HD + (int64_t)h * HD + c] = rb::from_f<T>(ag * f);
+    } else {
+      const int64_t o = ((int64_t)b * p.H + h) * fp.splits + split;
+      fp.part_acc[o * HD + c] = ag;
+      if (c == 0) { fp.part_ml[o * 2] = mg; fp.part_ml[o * 2 + 1] = lg; }
+    }
+  }
+}
+
+template <typename T, int HD>
+__global__ void sink_window_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, const T* __restrict__ qkvg,
+                                                int64_t ld, int og, int H, int gate, T* __restrict__ out, int splits) {
+  const int64_t bh = blockIdx.x;
+  const int c = threadIdx.x;
+  float mg = -INFINITY;
+  for (int s = 0; s < splits; ++s) mg = fmaxf(mg, part_ml[(bh * splits + s) * 2]);
+  float lg = 0.f, ag = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(bh * splits + s) * 2];
+    const float cf = (ms == -INFINITY) ? 0.f : expf(ms - mg);
+    lg += part_ml[(bh * splits + s) * 2 + 1] * cf;
+    ag += part_acc[(bh * splits + s) * HD + c] * cf;
+  }
+  float f = lg > 0.f ? 1.f / lg : 0.f;
+  if (gate) f *= 1.f / (1.f + expf(-rb::to_f(qkvg[(bh / H) * ld + og + (bh % H)])));
+  out[bh * HD + c] = rb::from_f<T>(ag * f);
+}
+
+template <typename T, int HD>
+int launch_fast(const FastParams& fp, int B, cudaStream_t s) {
+  const DecodeParams& p = fp.d;
+  dim3 grid(B, p.G, fp.splits);
+#define RB_L(REP) sink_window_decode_fast_kernel<T, HD, REP><<<grid, kFastThreads, 0, s>>>(fp)
+  switch (p.H / p.G) {
+    case 1: RB_L(1); break;
+    case 2: RB_L(2); break;
+    case 4: RB_L(4); break;
+    case 8: RB_L(8); break;
+    default: return -1;
+  }
+#undef RB_L
+  if (fp.splits > 1)
+    sink_window_decode_merge_kernel<T, HD><<<B * p.H, HD, 0, s>>>(fp.part_acc, fp.part_ml, reinterpret_cast<const T*>(p.qkvg), p.ld,
+                                                                  p.H * HD + 2 * p.G * HD, p.H, p.gate, reinterpret_cast<T*>(p.out), fp.splits);
+  return 0;
+}
+
 }  // namespace
 
 extern "C" int rb_value_norm_store(const void* qkvg, int64_t ld, int dt, void* vout, void* kc, void* vc, const int* tok_slot, const int* pos,
@@ -395,4 +621,19 @@ extern "C" int rb_sink_window_decode(const void* qkvg, int64_t ld, void* out, co
   if (smem > 48 * 1024) cudaFuncSetAttribute(sink_window_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   sink_window_decode_kernel<<<dim3(B, G), kDecThreads, smem, s>>>(p);
   return 0;
+}
+
+// 16-bit fast path of the decode form (dt 1 / 2, d == dv in {64, 128}, H / G in {1, 2, 4, 8}, 16-byte aligned rows); part_acc
+// [B, H, splits, d] and part_ml [B, H, splits, 2] fp32 are scratch for splits > 1.  Returns -1 for shapes it does not take.
+extern "C" int rb_sink_window_decode_fast(const void* qkvg, int64_t ld, void* out, const void* temp, const void* sink, void* kc, void* vc,
+                                          const int* lens, const int* slots, float* part_acc, float* part_ml, int splits, int B, int H, int G, int d,
+                                          int rows, float scale, int window, int keep, float slope_base, int gate, int do_norm, float eps, int dt,
+                                          cudaStream_t s) {
+  if (B == 0) return 0;
+  if ((dt != 1 && dt != 2) || (d != 64 && d != 128) || H % G || ld % 8 || ((uintptr_t)qkvg & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15))
+    return -1;
+  FastParams fp{DecodeParams{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, d, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps},
+                part_acc, part_ml, splits};
+  if (dt == 1) return d == 128 ? launch_fast<__nv_bfloat16, 128>(fp, B, s) : launch_fast<__nv_bfloat16, 64>(fp, B, s);
+  return d == 128 ? launch_fast<__half, 128>(fp, B, s) : launch_fast<__half, 64>(fp, B, s);
 }

@@ -234,6 +234,35 @@ def test_window_attention_prefill_cache_then_decode(device, dtype, H, G, d, dv, 
     assert worst < (2e-5 if dtype == torch.float32 else 0.03), worst
 
 
+@pytest.mark.parametrize("device,dtype", ALL)
+@pytest.mark.parametrize("H,G,d,window,keep,S", [(4, 2, 64, None, 0, 1024), (2, 2, 128, 384, 10, 2048), (8, 1, 64, 300, 200, 600)])
+def test_window_decode_long_context_key_splits(device, dtype, H, G, d, window, keep, S):
+    """Contexts of hundreds of keys (the 16-bit decode kernel cuts them into several ranges and merges the partial softmaxes), rings
+    that wrap while decoding, unequal rows in one batch."""
+    prompt, total = [500, 3, 390], [530, 33, 420]
+    a, m, qkvg, temp, sink = attn_case(H, G, d, d, window, keep, d + H, dtype, total)
+    want = attn_oracle(a, m, qkvg, temp, sink, total)
+    rows = a.cache_rows(S)
+    kc = torch.zeros(3, G, rows, d, dtype=dtype, device=device)
+    vc = torch.zeros(3, G, rows, d, dtype=dtype, device=device)
+    starts = [0, total[0], total[0] + total[1]]
+    slots = [1, 2, 0]
+    pre = torch.cat([qkvg[s:s + p] for s, p in zip(starts, prompt)]).to(device)
+    meta = pack_meta(prompt, device, slots)
+    A.value_norm_store(pre, a, 1e-5, kc, vc, meta.tok_slot, meta.pos, meta.remain)
+    cache_lens = torch.zeros(3, dtype=torch.int32, device=device)
+    cache_lens[torch.tensor(slots, device=device)] = torch.tensor(prompt, dtype=torch.int32, device=device)
+    sl = torch.tensor(slots, dtype=torch.int32, device=device)
+    worst = 0.0
+    for t in range(30):
+        rows_in = torch.stack([qkvg[starts[i] + prompt[i] + t] for i in range(3)]).to(device)
+        got = A.sink_window_decode_attention(rows_in, a, temp.to(device), sink.to(device), kc, vc, cache_lens, sl, 1e-5)
+        w = torch.stack([want[starts[i] + prompt[i] + t] for i in range(3)])
+        worst = max(worst, float((got.double().cpu() - w).abs().max() / w.abs().max()))
+        cache_lens[sl.long()] += 1
+    assert worst < (2e-5 if dtype == torch.float32 else 0.03), worst
+
+
 @pytest.mark.parametrize("device,dtype", EXACT)
 @pytest.mark.parametrize("mode", ["prompt", "decode"])
 def test_window_and_kept_edges_one_key_stands_out(device, dtype, mode):
