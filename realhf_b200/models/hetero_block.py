@@ -124,6 +124,23 @@ def loop_inject(model, i: int, x: torch.Tensor, x0: torch.Tensor) -> torch.Tenso
     return y.to(x.dtype)
 
 
+def _finish_block(model, i: int, b, x: torch.Tensor, y: torch.Tensor):
+    """x += mixer output y, then the feed-forward sublayer (same code for packed and one-token batches: neither has a state).  In
+    a plain pre-norm stack the add is fused into the feed-forward's norm."""
+    c, p = model.config, model.p
+    G, eps = c.norm_groups, c.layer_norm_epsilon
+    post = p.get(f"{i}.attn.ln_post.weight")
+    if b.mlp is None:
+        OF.residual_add_norm_(x, y, post, G, eps)
+        return
+    if post is None and G == 1:
+        h = OF.add_rms_norm_(x, y, p[f"{i}.mlp.ln.weight"], eps, model.dtype)
+    else:
+        OF.residual_add_norm_(x, y, post, G, eps)
+        h = OF.sublayer_input(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, model.dtype)
+    OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
+
+
 def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
     """Block i (1-based layer index; li = index among this stage's block runs) on the packed batch; x [T, H] is updated in place."""
     c, p = model.config, model.p
@@ -134,10 +151,7 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta) -> t
     if b.mixer != "latent_attention":
         h = OF.sublayer_input(x, p[f"{i}.attn.ln.weight"], G, eps, None, None, model.dtype)
         y = _window_attention_packed(model, i, li, h, meta) if b.mixer == "window_attention" else _delta_packed(model, i, li, h, meta)
-        OF.residual_add_norm_(x, y, p.get(f"{i}.attn.ln_post.weight"), G, eps)
-        if b.mlp is not None:
-            h = OF.sublayer_input(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, model.dtype)
-            OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
+        _finish_block(model, i, b, x, y)
         return x
     conv = meta.v[li] if keep and c.conv_taps else None
     h = OF.sublayer_input(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"), meta.pos, model.dtype,
@@ -174,10 +188,7 @@ def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.T
             y = _window_attention_decode(model, i, li, h, k_caches, v_caches, cache_lens, slots)
         else:
             y = _delta_decode(model, i, li, h, k_caches, v_caches, slots)
-        OF.residual_add_norm_(x, y, p.get(f"{i}.attn.ln_post.weight"), G, eps)
-        if b.mlp is not None:
-            h = OF.sublayer_input_step(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, slots, model.dtype)
-            OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
+        _finish_block(model, i, b, x, y)
         return x
     conv = v_caches[li] if c.conv_taps else None
     h = OF.sublayer_input_step(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"),

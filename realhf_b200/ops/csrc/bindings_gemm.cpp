@@ -256,7 +256,24 @@ Tensor gemm_glu_clamped(const Tensor& x, const Tensor& w, double limit, double a
   return act;
 }
 
+extern "C" int rb_gemm_2cta_act(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                                int in_dt, int act_kind, int num_sms, cudaStream_t s);
+
+// relu(x w^T)^2 with the activation in the epilogue of the CTA-pair GEMM (16-bit, more than one m-tile)
+Tensor gemm_relu2(const Tensor& x, const Tensor& w, int64_t num_sms) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && w.size(1) == x.size(1));
+  TORCH_CHECK(x.scalar_type() == w.scalar_type() && (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf));
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  c10::cuda::CUDAGuard g(x.device());
+  auto out = at::empty({M, N}, x.options());
+  int rc = rb_gemm_2cta_act(x.data_ptr(), w.data_ptr(), out.data_ptr(), nullptr, (int)M, (int)N, (int)K, x.stride(0), w.stride(0), N,
+                            x.scalar_type() == at::kBFloat16 ? 1 : 2, 1, (int)num_sms, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "gemm_relu2 failed: ", rc);
+  return out;
+}
+
 void register_gemm_ops(torch::Library& m) {
+  m.def("gemm_relu2(Tensor x, Tensor w, int num_sms) -> Tensor", &gemm_relu2);
   m.def("gemm_glu_clamped(Tensor x, Tensor w, float limit, float alpha, int num_sms) -> Tensor", &gemm_glu_clamped);
   m.def("gemm_glu(Tensor x, Tensor w, int act_kind, bool want_raw, int num_sms) -> Tensor[]", &gemm_glu);
   m.def("gemm_grouped_wgrad(Tensor dy, Tensor x, Tensor(a!) out, Tensor offsets, bool accumulate, int num_sms) -> ()", &gemm_grouped_wgrad);

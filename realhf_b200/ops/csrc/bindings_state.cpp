@@ -40,6 +40,7 @@ extern "C" {
 int rb_embed_sinusoid(const int64_t*, const void*, int, const int*, const int*, const float*, float*, int64_t, int, int, cudaStream_t);
 int rb_concat_cast(const void*, int, int, const void*, int, int, void*, int, int64_t, cudaStream_t);
 int rb_relu2(const void*, void*, int, int64_t, cudaStream_t);
+int rb_rms_norm_rows(void*, int, const void*, int, const void*, int, void*, int, int64_t, int, float, cudaStream_t);
 int rb_value_norm_store(const void*, int64_t, int, void*, void*, void*, const int*, const int*, const int*, int64_t, int, int, int, int, int, int, int,
                         float, cudaStream_t);
 int rb_sink_window_prefill(const void*, int64_t, const void*, void*, const void*, const void*, const int*, int, int, int, int, int, int, float, int,
@@ -83,6 +84,17 @@ Tensor relu2(const Tensor& x) {
   auto out = at::empty_like(x);
   TORCH_CHECK(rb_relu2(x.data_ptr(), out.data_ptr(), dt_code(x), x.numel(), cur_stream()) == 0);
   return out;
+}
+
+// out = rmsnorm(x) * w; with y: x += y in place first
+void rms_norm_rows(Tensor x, const OptT& y, const Tensor& w, Tensor out, double eps) {
+  CHECK_IN(x); CHECK_IN(w); CHECK_IN(out);
+  const int W = x.size(-1);
+  TORCH_CHECK(w.numel() == W && out.numel() == x.numel());
+  if (y.has_value()) { CHECK_IN((*y)); TORCH_CHECK(y->numel() == x.numel()); }
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(rb_rms_norm_rows(x.data_ptr(), dt_code(x), y.has_value() ? y->data_ptr() : nullptr, y.has_value() ? dt_code(*y) : 0, w.data_ptr(),
+                               dt_code(w), out.data_ptr(), dt_code(out), x.numel() / W, W, (float)eps, cur_stream()) == 0);
 }
 
 // caches: kc [n_slots, G, rows, d], vc [n_slots, G, rows, dv]
@@ -241,6 +253,7 @@ void register_state_ops(torch::Library& m) {
   m.def("embed_sinusoid(Tensor ids, Tensor wte, Tensor pos, Tensor? slots, Tensor inv_freq, Tensor(a!) out) -> ()", &embed_sinusoid);
   m.def("concat_cast(Tensor a, Tensor b, Tensor(a!) out) -> ()", &concat_cast);
   m.def("relu2(Tensor x) -> Tensor", &relu2);
+  m.def("rms_norm_rows(Tensor(a!) x, Tensor? y, Tensor w, Tensor(b!) out, float eps) -> ()", &rms_norm_rows);
   m.def("value_norm_store(Tensor qkvg, Tensor(a!) vout, Tensor(b!)? kc, Tensor(c!)? vc, Tensor? tok_slot, Tensor pos, Tensor? remain, int H, int G, int d, int dv, int keep, bool do_norm, float eps) -> ()", &value_norm_store);
   m.def("sink_window_attention(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, int dv, float scale, int window, int keep, float slope_base, bool gate) -> ()", &sink_window_attention);
   m.def("sink_window_attention_tc(Tensor qkvg, Tensor vn, Tensor(a!) out, Tensor? temp, Tensor? sink, Tensor cu, int max_seqlen, int H, int G, int d, float scale, int window, int keep, float slope_base, bool gate) -> ()", &sink_window_attention_tc);

@@ -85,6 +85,98 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const void* __restri
   }
 }
 
+// Packed form for long batches: a CTA owns 16 consecutive tokens x one unit of channels (a q or k head, a v head, or the 2H gate
+// scalars).  A thread keeps its channels' taps and a sliding window of the last taps - 1 inputs in registers and walks the tokens,
+// so every input is read once (plus a halo of taps - 1 rows per tile) and the weights once per CTA; the per-(token, head) sums of
+// squares are reduced per warp into shared memory and applied after one barrier.
+constexpr int kPT = 16, kPThreads = 128, kPCh = 2;   // tokens per tile, threads, channels per thread (units of up to 256 channels)
+
+__global__ void __launch_bounds__(kPThreads) delta_prepare_tiled_kernel(const void* __restrict__ proj, int64_t ld, int dt, const void* __restrict__ conv_w,
+                                                                        const void* __restrict__ A_log, const void* __restrict__ dt_bias,
+                                                                        float* __restrict__ u, const int* __restrict__ pos,
+                                                                        float* __restrict__ conv_state, const int* __restrict__ tok_slot,
+                                                                        const int* __restrict__ remain, int64_t T, int H, int G, int d, int dv,
+                                                                        int taps, float unit_eps) {
+  __shared__ float part[kPThreads / 32][kPT];
+  const int nqk = G * d, nv = H * dv, C = 2 * nqk + nv, UW = C + 2 * H;
+  const int unit = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t t0 = (int64_t)blockIdx.x * kPT;
+  const int nt = (int)min((int64_t)kPT, T - t0);
+  if (unit == 2 * G + H) {   // write strength and decay of every head
+    for (int idx = tid; idx < nt * H; idx += kPThreads) {
+      const int64_t t = t0 + idx / H;
+      const int h = idx % H;
+      const float b = ld_any(proj, dt, t * ld + C + nv + h);
+      u[t * UW + C + h] = 1.f / (1.f + expf(-b));
+      const float a = ld_any(proj, dt, t * ld + C + nv + H + h) + ld_any(dt_bias, dt, h);
+      const float sp = a > 20.f ? a : log1pf(expf(a));
+      u[t * UW + C + H + h] = expf(-expf(ld_any(A_log, dt, h)) * sp);
+    }
+    return;
+  }
+  const bool is_qk = unit < 2 * G;
+  const int us = is_qk ? d : dv;                       // channels of this unit
+  const int c_base = is_qk ? unit * d : 2 * nqk + (unit - 2 * G) * dv;
+  float w[kPCh][kMaxTaps], hist[kPCh][kMaxTaps - 1], yv[kPCh][kPT];
+  bool okc[kPCh];
+#pragma unroll
+  for (int ch = 0; ch < kPCh; ++ch) {
+    okc[ch] = tid + ch * kPThreads < us;
+    const int c = c_base + tid + ch * kPThreads;
+#pragma unroll
+    for (int back = 0; back < kMaxTaps; ++back)      // w[ch][back]: the tap that meets the input `back` tokens ago
+      w[ch][back] = (okc[ch] && back < taps) ? ld_any(conv_w, dt, (int64_t)c * taps + taps - 1 - back) : 0.f;
+#pragma unroll
+    for (int back = 1; back < kMaxTaps; ++back)
+      hist[ch][back - 1] = (okc[ch] && back < taps && t0 - back >= 0) ? ld_any(proj, dt, (t0 - back) * ld + c) : 0.f;
+  }
+#pragma unroll
+  for (int tt = 0; tt < kPT; ++tt) {
+    float ss = 0.f;
+    if (tt < nt) {
+      const int64_t t = t0 + tt;
+      const int p = pos[t];
+      const int slot = conv_state ? tok_slot[t] : -1;
+      const int rem = conv_state ? remain[t] : 0;
+#pragma unroll
+      for (int ch = 0; ch < kPCh; ++ch) {
+        const int c = c_base + tid + ch * kPThreads;
+        const float x = okc[ch] ? ld_any(proj, dt, t * ld + c) : 0.f;
+        float y = 0.f;
+#pragma unroll
+        for (int back = kMaxTaps - 1; back >= 1; --back)      // oldest first, the current token last: a fixed order
+          if (back < taps && back <= p) y = fmaf(hist[ch][back - 1], w[ch][back], y);
+        y = fmaf(x, w[ch][0], y);
+#pragma unroll
+        for (int back = kMaxTaps - 1; back >= 2; --back) hist[ch][back - 1] = hist[ch][back - 2];
+        hist[ch][0] = x;
+        if (okc[ch] && slot >= 0 && taps > 1 && rem < taps - 1) conv_state[((int64_t)slot * (taps - 1) + (taps - 2 - rem)) * C + c] = x;
+        y = y / (1.f + expf(-y));
+        yv[ch][tt] = y;
+        ss = fmaf(y, y, ss);
+      }
+    }
+    if (is_qk) {
+      ss = rb::warp_sum(ss);
+      if (lane == 0) part[warp][tt] = ss;
+    }
+  }
+  if (is_qk) __syncthreads();
+#pragma unroll
+  for (int tt = 0; tt < kPT; ++tt) {
+    if (tt < nt) {
+      float r = 1.f;
+      if (is_qk) {
+        r = 1.f / sqrtf(part[0][tt] + part[1][tt] + part[2][tt] + part[3][tt] + unit_eps);
+        if (unit < G) r *= 1.f / sqrtf((float)d);
+      }
+#pragma unroll
+      for (int ch = 0; ch < kPCh; ++ch)
+        if (okc[ch]) u[(t0 + tt) * UW + c_base + tid + ch * kPThreads] = yv[ch][tt] * r;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ recurrence
 constexpr int kScanThreads = 128, kEPL = 32, kTok = 8;
 
@@ -191,6 +283,12 @@ extern "C" int rb_delta_prepare(const void* proj, int64_t ld, int dt, const void
   if (T == 0) return 0;
   if (taps < 1 || taps > kMaxTaps) return -1;
   const int C = 2 * G * d + H * dv;
+  if (pos != nullptr && T >= 64 && d <= kPCh * kPThreads && dv <= kPCh * kPThreads) {
+    dim3 grid((unsigned)((T + kPT - 1) / kPT), 2 * G + H + 1);
+    delta_prepare_tiled_kernel<<<grid, kPThreads, 0, s>>>(proj, ld, dt, conv_w, A_log, dt_bias, u, pos, conv_state, tok_slot, remain, T, H, G, d, dv,
+                                                          taps, unit_eps);
+    return 0;
+  }
   const size_t smem = sizeof(float) * (size_t)C;
   if (smem > 200 * 1024) return -2;
   if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -275,6 +275,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_2cta_kernel(const __grid_con
 #pragma unroll
             for (int i = 0; i < 32; ++i) if (i < n_valid) v[i] += rb::to_f(bias[col + i]);
           }
+          if (p.unary_act == 1) {  // relu(x)^2 on the value the unfused path would have stored
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { const float a = fmaxf(rb::to_f(rb::from_f<OutT>(v[i])), 0.f); v[i] = a * a; }
+          }
           OutT* dst = Cp + (int64_t)row * p.ldc + col;
           if (p.accumulate) {
 #pragma unroll
@@ -413,6 +417,27 @@ int rb_gemm_2cta_glu_ex(const void* A, const void* B, void* act, void* raw, int 
   Params p{act, nullptr, ld_act, M, F, K, 0, nullptr, 0, 1, 0, nullptr, F, act_kind, raw, ld_raw, limit, alpha};
   if (in_dt == 1) return launch2<256, false, false, __nv_bfloat16, 1, true>(ta, tb, p, num_sms, s);
   return launch2<256, false, false, __half, 0, true>(ta, tb, p, num_sms, s);
+}
+
+// C[M, N] = act(A[M, K] x B[N, K]^T (+ bias)) with a unary activation in the epilogue (act_kind 1: relu(x)^2); 16-bit in and out.
+// Returns -40 when the problem has a single m-tile (the caller composes GEMM + activation kernel instead).
+int rb_gemm_2cta_act(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int in_dt,
+                     int act_kind, int num_sms, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (in_dt != 1 && in_dt != 2) return -10;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -11;
+  if (M <= BM) return -40;
+  if (num_sms <= 0) num_sms = rb::kNumSMs;
+  const int bn = N > 128 ? 256 : 128;
+  CUtensorMap ta, tb;
+  const int bf = in_dt == 1;
+  bool ok = make_tmap(&ta, A, bf, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BK, (uint32_t)BM);
+  ok = ok && make_tmap(&tb, B, bf, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BK, (uint32_t)(bn / 2));
+  if (!ok) return -13;
+  Params p{C, bias, ldc, M, N, K, 0, nullptr, 0, 1, 0, nullptr, 0, 0, nullptr, 0, 0.f, 0.f, act_kind};
+  if (in_dt == 1)
+    return bn == 256 ? launch2<256, false, false, __nv_bfloat16, 1>(ta, tb, p, num_sms, s) : launch2<128, false, false, __nv_bfloat16, 1>(ta, tb, p, num_sms, s);
+  return bn == 256 ? launch2<256, false, false, __half, 0>(ta, tb, p, num_sms, s) : launch2<128, false, false, __half, 0>(ta, tb, p, num_sms, s);
 }
 
 int rb_gemm_2cta_glu(const void* A, const void* B, void* act, void* raw, int M, int F, int K, int64_t lda, int64_t ldb, int64_t ld_act,

@@ -36,6 +36,8 @@ struct Params {
   int64_t ld_raw;
   float glu_limit;   // L and alpha of the clamped form
   float glu_alpha;
+  // optional unary activation on the plain (non-GLU) epilogue of the 2-CTA kernel, after the bias: 0 none, 1 relu(x)^2
+  int unary_act;
 };
 
 template <typename T> RB_DEVICE void store_chunk(T* dst, const float* v, int n_valid, bool vec_ok);

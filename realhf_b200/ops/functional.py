@@ -630,6 +630,10 @@ def sublayer_input(x, w, groups: int, eps: float, conv_w, pos, out_dtype, state=
     h = n.  With `state` [n_slots, taps - 1, W] fp32, the n of the last taps - 1 tokens of every sequence is left in
     state[tok_slot[t]] (oldest first; rows of a shorter sequence are not written, the slot manager zeroes them), `remain[t]`
     being the number of tokens that follow t in its sequence."""
+    if use_native(x) and groups == 1 and conv_w is None:     # a plain RMSNorm: one CTA per row
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        lib().rms_norm_rows(x.contiguous(), None, w, out, eps)
+        return out
     if use_native(x) and (conv_w is None or conv_w.shape[1] <= 8) and groups * 32 <= 48 * 1024:   # the kernels hold <= 8 taps
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         lib().sublayer_input(x.contiguous(), w, _tap_major(conv_w), pos, out, state if conv_w is not None else None,
@@ -654,6 +658,10 @@ def sublayer_input_step_ref(x, w, groups, eps, conv_w, state, slots, out_dtype):
 def sublayer_input_step(x, w, groups: int, eps: float, conv_w, state, slots, out_dtype):
     """Decode form of `sublayer_input` (one token per row): the earlier inputs come from state[slots[b]] ([taps - 1, W] fp32,
     oldest first), which is then shifted by one with this token's n appended.  slots None = row b uses slot b."""
+    if use_native(x) and groups == 1 and conv_w is None:
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        lib().rms_norm_rows(x.contiguous(), None, w, out, eps)
+        return out
     if use_native(x) and (conv_w is None or conv_w.shape[1] <= 8) and groups * 32 <= 48 * 1024:
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         lib().sublayer_input_step(x.contiguous(), w, _tap_major(conv_w), out, state if conv_w is not None else None, slots, groups, eps)
@@ -738,6 +746,17 @@ def embed_sinusoid(ids, wte, pos, base: float = 10000.0, slots=None):
     return embed_sinusoid_ref(ids, wte, pos if slots is None else pos[slots.long()], inv_freq[1])
 
 
+def add_rms_norm_(x, y, w, eps: float, out_dtype):
+    """x <- x + y in place (fp32 sum, stored in x's dtype), then RMSNorm(x) * w in out_dtype: the residual add of one sublayer fused
+    into the norm of the next."""
+    if use_native(x) and x.is_contiguous():
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        lib().rms_norm_rows(x, y.contiguous(), w, out, eps)
+        return out
+    x.copy_((x.float() + y.float()).to(x.dtype))
+    return group_rmsnorm_ref(x, w, 1, eps).to(out_dtype)
+
+
 def relu2(x):
     """relu(x)^2, elementwise, in x's dtype (fp32 inside)."""
     if use_native(x):
@@ -747,7 +766,17 @@ def relu2(x):
 
 
 def relu2_linear(x, w_up):
-    """relu(x @ w_up^T)^2."""
+    """relu(x @ w_up^T)^2.  16-bit CUDA operands of more than 128 rows run projection and activation as ONE kernel (the activation
+    in the epilogue of the CTA-pair tcgen05 GEMM, like `gated_linear`); everything else composes the two ops."""
+    if use_native(x) and x.dtype in (torch.bfloat16, torch.float16) and gemm_impl() is not None:
+        from realhf_b200.ops import gemm as G
+        x2 = x.reshape(-1, x.shape[-1])
+        if (gemm_impl() is G.linear and G.supported(x2, w_up) and x2.shape[0] > 128 and w_up.shape[0] % 8 == 0 and w_up.is_contiguous()
+                and os.environ.get("REAL_GEMM_GLU", "1") == "1"):
+            if x2.stride(-1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+                x2 = x2.contiguous()
+            out = lib().gemm_relu2(x2, w_up, G._sms(x.device))
+            return out.view(*x.shape[:-1], w_up.shape[0])
     return relu2(linear(x, w_up))
 
 

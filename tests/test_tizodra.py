@@ -396,6 +396,53 @@ def test_delta_rule_prefill_then_decode(device, dtype, H, G, d, dv, taps):
     assert worst < (5e-5 if dtype == torch.float32 else 0.08), worst
 
 
+@pytest.mark.parametrize("device,dtype", ALL)
+@pytest.mark.parametrize("H,G,d,dv,taps", [(4, 2, 8, 16, 4), (2, 2, 128, 136, 2), (3, 1, 160, 40, 1), (2, 1, 64, 64, 5)])
+def test_delta_prepare_long_packed_batch(device, dtype, H, G, d, dv, taps):
+    """Batches long enough for the token-tiled kernel: sequences that start and end inside a tile, the convolution history left in
+    the slots, and the same rows through the per-token form (a short batch)."""
+    lens = [70, 1, 33, 16, 100, 2]
+    slots = [2, 5, 0, 1, 4, 3]
+    dl, proj, conv_w, A_log, dt_bias = delta_case(H, G, d, dv, taps, 3 * H + d, dtype, sum(lens))
+    ins = delta_oracle_inputs(dl, proj, conv_w, A_log, dt_bias, lens)
+    want = torch.cat([torch.cat([x[0].reshape(n, -1), x[1].reshape(n, -1), x[2].reshape(n, -1), x[3], x[4]], -1) for x, n in zip(ins, lens)])
+    C = dl.conv_channels
+    dev = lambda t: t.to(device)
+    state = torch.full((6, taps - 1, C), 5.0, device=device)
+    meta = pack_meta(lens, device, slots)
+    u = R.delta_prepare(dev(proj), dev(conv_w), dev(A_log), dev(dt_bias), dl, meta.pos, state, meta.tok_slot, meta.remain)
+    assert close(u, want, dtype, 2e-6, 0.03)
+    off = 0
+    for n, sl in zip(lens, slots):
+        have = min(n, taps - 1)
+        if have:
+            assert torch.equal(state[sl, taps - 1 - have:].cpu(), proj[off + n - have:off + n, :C].float())
+        assert bool((state[sl, : taps - 1 - have] == 5.0).all())                      # rows of a shorter sequence are left alone
+        off += n
+    meta = pack_meta(lens[2:4], device)
+    short = R.delta_prepare(dev(proj[71:120]), dev(conv_w), dev(A_log), dev(dt_bias), dl, meta.pos)
+    assert close(short, u[71:120].double().cpu(), dtype, 2e-6, 2e-6)
+
+
+@pytest.mark.parametrize("device,dtype", ALL)
+def test_fused_relu2_projection_and_add_norm(device, dtype):
+    g = torch.Generator().manual_seed(11)
+    for T, W, F_ in ((300, 64, 96), (40, 64, 96), (513, 128, 264)):
+        x = torch.randn(T, W, generator=g).to(dtype)
+        w = (torch.randn(F_, W, generator=g) / math.sqrt(W)).to(dtype)
+        want = torch.relu(x.to(F64) @ w.to(F64).T) ** 2
+        assert close(OF.relu2_linear(x.to(device), w.to(device)), want, dtype, 1e-5, 0.03)
+    x = torch.randn(37, 48, generator=g) * 3
+    y = torch.randn(37, 48, generator=g).to(dtype)
+    nw = (1 + 0.2 * torch.randn(48, generator=g)).to(dtype)
+    xs = x.to(device).clone()
+    h = OF.add_rms_norm_(xs, y.to(device), nw.to(device), 1e-5, dtype)
+    s = x.to(F64) + y.to(F64)
+    assert xs.dtype == torch.float32 and close(xs, s, torch.float32, 1e-6)
+    assert h.dtype == dtype and close(h, O.rms_norm(s, nw.to(F64), 1e-5), dtype, 1e-5, 0.02)
+    assert close(OF.sublayer_input(xs, nw.to(device), 1, 1e-5, None, None, dtype), O.rms_norm(s, nw.to(F64), 1e-5), dtype, 1e-5, 0.02)
+
+
 @pytest.mark.parametrize("device,dtype", EXACT)
 @pytest.mark.parametrize("mode", ["prompt", "decode"])
 def test_delta_state_keeps_a_far_write(device, dtype, mode):
