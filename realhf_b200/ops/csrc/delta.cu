@@ -89,8 +89,9 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const void* __restri
 // scalars).  A thread keeps its channels' taps and a sliding window of the last taps - 1 inputs in registers and walks the tokens,
 // so every input is read once (plus a halo of taps - 1 rows per tile) and the weights once per CTA; the per-(token, head) sums of
 // squares are reduced per warp into shared memory and applied after one barrier.
-constexpr int kPT = 16, kPThreads = 128, kPCh = 2;   // tokens per tile, threads, channels per thread (units of up to 256 channels)
+constexpr int kPT = 16, kPThreads = 128;   // tokens per tile, threads; CH channels per thread (units of up to CH * 128 channels)
 
+template <int CH>
 __global__ void __launch_bounds__(kPThreads) delta_prepare_tiled_kernel(const void* __restrict__ proj, int64_t ld, int dt, const void* __restrict__ conv_w,
                                                                         const void* __restrict__ A_log, const void* __restrict__ dt_bias,
                                                                         float* __restrict__ u, const int* __restrict__ pos,
@@ -117,12 +118,18 @@ __global__ void __launch_bounds__(kPThreads) delta_prepare_tiled_kernel(const vo
   const bool is_qk = unit < 2 * G;
   const int us = is_qk ? d : dv;                       // channels of this unit
   const int c_base = is_qk ? unit * d : 2 * nqk + (unit - 2 * G) * dv;
-  float w[kPCh][kMaxTaps], hist[kPCh][kMaxTaps - 1], yv[kPCh][kPT];
-  bool okc[kPCh];
+  // all loads of the tile first (independent, in flight together), then the arithmetic
+  int ps[kPT];
 #pragma unroll
-  for (int ch = 0; ch < kPCh; ++ch) {
+  for (int tt = 0; tt < kPT; ++tt) ps[tt] = tt < nt ? pos[t0 + tt] : 0;
+  float w[CH][kMaxTaps], hist[CH][kMaxTaps - 1], xv[CH][kPT];
+  bool okc[CH];
+#pragma unroll
+  for (int ch = 0; ch < CH; ++ch) {
     okc[ch] = tid + ch * kPThreads < us;
     const int c = c_base + tid + ch * kPThreads;
+#pragma unroll
+    for (int tt = 0; tt < kPT; ++tt) xv[ch][tt] = (okc[ch] && tt < nt) ? ld_any(proj, dt, (t0 + tt) * ld + c) : 0.f;
 #pragma unroll
     for (int back = 0; back < kMaxTaps; ++back)      // w[ch][back]: the tap that meets the input `back` tokens ago
       w[ch][back] = (okc[ch] && back < taps) ? ld_any(conv_w, dt, (int64_t)c * taps + taps - 1 - back) : 0.f;
@@ -130,18 +137,27 @@ __global__ void __launch_bounds__(kPThreads) delta_prepare_tiled_kernel(const vo
     for (int back = 1; back < kMaxTaps; ++back)
       hist[ch][back - 1] = (okc[ch] && back < taps && t0 - back >= 0) ? ld_any(proj, dt, (t0 - back) * ld + c) : 0.f;
   }
+  if (conv_state != nullptr && taps > 1) {
+#pragma unroll
+    for (int tt = 0; tt < kPT; ++tt) {
+      if (tt < nt) {
+        const int slot = tok_slot[t0 + tt], rem = remain[t0 + tt];
+        if (slot >= 0 && rem < taps - 1) {
+#pragma unroll
+          for (int ch = 0; ch < CH; ++ch)
+            if (okc[ch]) conv_state[((int64_t)slot * (taps - 1) + (taps - 2 - rem)) * C + c_base + tid + ch * kPThreads] = xv[ch][tt];
+        }
+      }
+    }
+  }
 #pragma unroll
   for (int tt = 0; tt < kPT; ++tt) {
     float ss = 0.f;
     if (tt < nt) {
-      const int64_t t = t0 + tt;
-      const int p = pos[t];
-      const int slot = conv_state ? tok_slot[t] : -1;
-      const int rem = conv_state ? remain[t] : 0;
+      const int p = ps[tt];
 #pragma unroll
-      for (int ch = 0; ch < kPCh; ++ch) {
-        const int c = c_base + tid + ch * kPThreads;
-        const float x = okc[ch] ? ld_any(proj, dt, t * ld + c) : 0.f;
+      for (int ch = 0; ch < CH; ++ch) {
+        const float x = xv[ch][tt];
         float y = 0.f;
 #pragma unroll
         for (int back = kMaxTaps - 1; back >= 1; --back)      // oldest first, the current token last: a fixed order
@@ -150,9 +166,8 @@ __global__ void __launch_bounds__(kPThreads) delta_prepare_tiled_kernel(const vo
 #pragma unroll
         for (int back = kMaxTaps - 1; back >= 2; --back) hist[ch][back - 1] = hist[ch][back - 2];
         hist[ch][0] = x;
-        if (okc[ch] && slot >= 0 && taps > 1 && rem < taps - 1) conv_state[((int64_t)slot * (taps - 1) + (taps - 2 - rem)) * C + c] = x;
         y = y / (1.f + expf(-y));
-        yv[ch][tt] = y;
+        xv[ch][tt] = y;
         ss = fmaf(y, y, ss);
       }
     }
@@ -171,8 +186,8 @@ __global__ void __launch_bounds__(kPThreads) delta_prepare_tiled_kernel(const vo
         if (unit < G) r *= 1.f / sqrtf((float)d);
       }
 #pragma unroll
-      for (int ch = 0; ch < kPCh; ++ch)
-        if (okc[ch]) u[(t0 + tt) * UW + c_base + tid + ch * kPThreads] = yv[ch][tt] * r;
+      for (int ch = 0; ch < CH; ++ch)
+        if (okc[ch]) u[(t0 + tt) * UW + c_base + tid + ch * kPThreads] = xv[ch][tt] * r;
     }
   }
 }
@@ -188,10 +203,13 @@ struct ScanParams {
   int H, G, d, dv, step;
 };
 
+// Row mapping: lane l of a column's LPC lanes holds the state rows ((e / 4) * LPC + l) * 4 + e % 4, e = 0 .. 31, so that its q / k
+// operands are 8 aligned float4 reads of shared memory per token (the lanes of a column read neighbouring float4s, the columns of
+// a warp the same ones).  Dot products run on four independent accumulators.
 template <int LPC>
-__global__ void __launch_bounds__(kScanThreads) delta_rule_kernel(ScanParams p) {
+__global__ void __launch_bounds__(kScanThreads, 3) delta_rule_kernel(ScanParams p) {
   constexpr int NCOL = kScanThreads / LPC;
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * NCOL;
   const int g = h / (p.H / p.G), d = p.d, dv = p.dv;
   const int nqk = p.G * d, C = 2 * nqk + p.H * dv, UW = C + 2 * p.H;
@@ -202,45 +220,82 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_kernel(ScanParams p) 
   if (t1 <= t0) return;
   const int slot = p.s_state == nullptr ? -1 : (p.slots ? p.slots[seq] : (p.step ? seq : -1));
   float* S_g = slot >= 0 ? p.s_state + (((int64_t)slot * p.H + h) * d) * dv : nullptr;
-  const int dpad = kEPL * LPC;                    // rows e * LPC + l; rows >= d hold zeros and read zero q / k
-  float* qs = sm;                                 // [kTok][dpad]
-  float* ks = qs + kTok * dpad;                   // [kTok][dpad]
-  float* vs = ks + kTok * dpad;                   // [kTok][NCOL]
-  float* bg = vs + kTok * NCOL;                   // [kTok][2]  beta, g
+  constexpr int dpad = kEPL * LPC;                // rows >= d hold zeros and read zero q / k
+  constexpr int kBuf = 2 * kTok * dpad + kTok * NCOL + 2 * kTok;   // floats of one staging buffer: q, k, v, (beta, g)
+  constexpr int NQ = kTok * dpad / kScanThreads, NV = (kTok * NCOL + kScanThreads - 1) / kScanThreads;
+  auto row_of = [&](int e) { return ((e >> 2) * LPC + l) * 4 + (e & 3); };
   float S[kEPL];
 #pragma unroll
   for (int e = 0; e < kEPL; ++e) {
-    const int row = e * LPC + l;
+    const int row = row_of(e);
     S[e] = (p.step && S_g && active && row < d) ? S_g[(int64_t)row * dv + col] : 0.f;
   }
-  for (int tb = t0; tb < t1; tb += kTok) {
+  // The inputs of the next 8 tokens are fetched into registers while the current 8 are processed out of shared memory (two
+  // staging buffers, one barrier per chunk).
+  float rq[NQ], rk[NQ], rv[NV], rb = 0.f;
+  auto fetch = [&](int tb) {
     const int nt = min(kTok, t1 - tb);
-    __syncthreads();
-    for (int idx = tid; idx < nt * dpad; idx += kScanThreads) {
-      const int tt = idx / dpad, e = idx % dpad;
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      const int idx = tid + i * kScanThreads, tt = idx / dpad, e = idx % dpad;
+      const bool ok = tt < nt && e < d;
       const float* row = p.u + (int64_t)(tb + tt) * UW;
-      qs[idx] = e < d ? row[g * d + e] : 0.f;
-      ks[idx] = e < d ? row[nqk + g * d + e] : 0.f;
+      rq[i] = ok ? row[g * d + e] : 0.f;
+      rk[i] = ok ? row[nqk + g * d + e] : 0.f;
     }
-    for (int idx = tid; idx < nt * NCOL; idx += kScanThreads) {
-      const int tt = idx / NCOL, c = c0 + idx % NCOL;
-      vs[idx] = c < dv ? p.u[(int64_t)(tb + tt) * UW + 2 * nqk + h * dv + c] : 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int idx = tid + i * kScanThreads, tt = idx / NCOL, c = c0 + idx % NCOL;
+      rv[i] = (idx < kTok * NCOL && tt < nt && c < dv) ? p.u[(int64_t)(tb + tt) * UW + 2 * nqk + h * dv + c] : 0.f;
     }
-    if (tid < nt * 2) bg[tid] = p.u[(int64_t)(tb + tid / 2) * UW + C + (tid & 1) * p.H + h];
+    rb = tid < nt * 2 ? p.u[(int64_t)(tb + tid / 2) * UW + C + (tid & 1) * p.H + h] : 0.f;
+  };
+  auto stage = [&](float* buf) {
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) { buf[tid + i * kScanThreads] = rq[i]; buf[kTok * dpad + tid + i * kScanThreads] = rk[i]; }
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (tid + i * kScanThreads < kTok * NCOL) buf[2 * kTok * dpad + tid + i * kScanThreads] = rv[i];
+    if (tid < 2 * kTok) buf[2 * kTok * dpad + kTok * NCOL + tid] = rb;
+  };
+  fetch(t0);
+  int which = 0;
+  for (int tb = t0; tb < t1; tb += kTok, which ^= 1) {
+    const int nt = min(kTok, t1 - tb);
+    float* buf = sm + which * kBuf;
+    stage(buf);
     __syncthreads();
+    if (tb + kTok < t1) fetch(tb + kTok);
+    const float* qs = buf;
+    const float* ks = buf + kTok * dpad;
+    const float* vs = ks + kTok * dpad;
+    const float* bg = vs + kTok * NCOL;
     for (int tt = 0; tt < nt; ++tt) {
       const float beta = bg[tt * 2], gg = bg[tt * 2 + 1];
-      const float* kq = ks + tt * dpad + l;
-      const float* qq = qs + tt * dpad + l;
-      float acc = 0.f;
+      const float4* kq = reinterpret_cast<const float4*>(ks + tt * dpad) + l;
+      const float4* qq = reinterpret_cast<const float4*>(qs + tt * dpad) + l;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int e = 0; e < kEPL; ++e) { S[e] *= gg; acc = fmaf(S[e], kq[e * LPC], acc); }
+      for (int e4 = 0; e4 < kEPL / 4; ++e4) {
+        const float4 kk = kq[e4 * LPC];
+        S[e4 * 4] *= gg; S[e4 * 4 + 1] *= gg; S[e4 * 4 + 2] *= gg; S[e4 * 4 + 3] *= gg;
+        a0 = fmaf(S[e4 * 4], kk.x, a0); a1 = fmaf(S[e4 * 4 + 1], kk.y, a1);
+        a2 = fmaf(S[e4 * 4 + 2], kk.z, a2); a3 = fmaf(S[e4 * 4 + 3], kk.w, a3);
+      }
+      float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
       for (int off = 1; off < LPC; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
       const float w = beta * (vs[tt * NCOL + tid / LPC] - acc);
-      float ov = 0.f;
+      a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
-      for (int e = 0; e < kEPL; ++e) { S[e] = fmaf(kq[e * LPC], w, S[e]); ov = fmaf(S[e], qq[e * LPC], ov); }
+      for (int e4 = 0; e4 < kEPL / 4; ++e4) {
+        const float4 kk = kq[e4 * LPC], q4 = qq[e4 * LPC];
+        S[e4 * 4] = fmaf(kk.x, w, S[e4 * 4]); S[e4 * 4 + 1] = fmaf(kk.y, w, S[e4 * 4 + 1]);
+        S[e4 * 4 + 2] = fmaf(kk.z, w, S[e4 * 4 + 2]); S[e4 * 4 + 3] = fmaf(kk.w, w, S[e4 * 4 + 3]);
+        a0 = fmaf(S[e4 * 4], q4.x, a0); a1 = fmaf(S[e4 * 4 + 1], q4.y, a1);
+        a2 = fmaf(S[e4 * 4 + 2], q4.z, a2); a3 = fmaf(S[e4 * 4 + 3], q4.w, a3);
+      }
+      float ov = (a0 + a1) + (a2 + a3);
 #pragma unroll
       for (int off = 1; off < LPC; off <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, off);
       if (active && l == 0) p.o[((int64_t)(tb + tt) * p.H + h) * dv + col] = ov;
@@ -249,7 +304,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_kernel(ScanParams p) 
   if (S_g && active) {
 #pragma unroll
     for (int e = 0; e < kEPL; ++e) {
-      const int row = e * LPC + l;
+      const int row = row_of(e);
       if (row < d) S_g[(int64_t)row * dv + col] = S[e];
     }
   }
@@ -283,10 +338,14 @@ extern "C" int rb_delta_prepare(const void* proj, int64_t ld, int dt, const void
   if (T == 0) return 0;
   if (taps < 1 || taps > kMaxTaps) return -1;
   const int C = 2 * G * d + H * dv;
-  if (pos != nullptr && T >= 64 && d <= kPCh * kPThreads && dv <= kPCh * kPThreads) {
+  if (pos != nullptr && T >= 64 && d <= 2 * kPThreads && dv <= 2 * kPThreads) {
     dim3 grid((unsigned)((T + kPT - 1) / kPT), 2 * G + H + 1);
-    delta_prepare_tiled_kernel<<<grid, kPThreads, 0, s>>>(proj, ld, dt, conv_w, A_log, dt_bias, u, pos, conv_state, tok_slot, remain, T, H, G, d, dv,
-                                                          taps, unit_eps);
+    if (d <= kPThreads && dv <= kPThreads)
+      delta_prepare_tiled_kernel<1><<<grid, kPThreads, 0, s>>>(proj, ld, dt, conv_w, A_log, dt_bias, u, pos, conv_state, tok_slot, remain, T, H, G, d,
+                                                               dv, taps, unit_eps);
+    else
+      delta_prepare_tiled_kernel<2><<<grid, kPThreads, 0, s>>>(proj, ld, dt, conv_w, A_log, dt_bias, u, pos, conv_state, tok_slot, remain, T, H, G, d,
+                                                               dv, taps, unit_eps);
     return 0;
   }
   const size_t smem = sizeof(float) * (size_t)C;
@@ -304,7 +363,7 @@ extern "C" int rb_delta_rule(const float* u, float* o, const int* cu, float* s_s
   const int lpc = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8;
   const int ncol = kScanThreads / lpc;
   ScanParams p{u, o, cu, s_state, slots, H, G, d, dv, step};
-  const size_t smem = sizeof(float) * ((size_t)2 * kTok * kEPL * lpc + (size_t)kTok * ncol + 2 * kTok);
+  const size_t smem = 2 * sizeof(float) * ((size_t)2 * kTok * kEPL * lpc + (size_t)kTok * ncol + 2 * kTok);   // two staging buffers
   dim3 grid(n_seqs, H, RB_CEIL_DIV(dv, ncol));
   switch (lpc) {
     case 1: delta_rule_kernel<1><<<grid, kScanThreads, smem, s>>>(p); break;
