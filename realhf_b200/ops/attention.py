@@ -442,7 +442,7 @@ def sink_window_attention(qkvg, v_n, a, temp, sink, pos, cu_seqlens, max_seqlen=
     """Packed causal attention of a window-attention block over the batch's own keys (every sequence starts at position 0):
     softmax_j(q_i . k_j * scale * temp_h - slope_h (i - j)) with the sink logit in the denominator, over j <= i with
     i - j < window or j < keep_first; head h's output times sigmoid(gate logit h).  Returns [T, H * dv] in the model dtype."""
-    if use_native(qkvg):
+    if use_native(qkvg) and a.qk_dim <= 512 and a.v_dim <= 256:     # (larger heads: the PyTorch form, on the device)
         T = qkvg.shape[0]
         out = torch.empty(T, a.n_heads * a.v_dim, dtype=qkvg.dtype, device=qkvg.device)
         if max_seqlen is None:
@@ -498,7 +498,7 @@ def sink_window_decode_attention(qkvg, a, temp, sink, k_cache, v_cache, cache_le
     """One new token per row against the caches of its slot (slots None: row b is slot b).  The row's key and normalised value
     are appended in place at the row of position cache_lens[slot] (cache_lens itself is not changed), then the token attends to
     every cached position its window and `keep_first` allow, itself included.  Returns [B, H * dv] in the model dtype."""
-    if use_native(qkvg):
+    if use_native(qkvg) and a.v_dim <= 256:
         B = qkvg.shape[0]
         out = torch.empty(B, a.n_heads * a.v_dim, dtype=qkvg.dtype, device=qkvg.device)
         lib().sink_window_decode_attention(qkvg, out, temp, sink, k_cache, v_cache, cache_lens, slots, a.n_heads, a.n_kv_heads, a.qk_dim,

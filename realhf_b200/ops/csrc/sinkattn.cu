@@ -218,7 +218,9 @@ struct DecodeParams {
 __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeParams p) {
   extern __shared__ __align__(16) float smem[];
   const int b = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int rep = p.H / p.G, d = p.d, dv = p.dv, dt = p.dt;
+  // blockIdx.z: a chunk of up to kMaxRep query heads of the group (every chunk's CTA appends the same new row)
+  const int group = p.H / p.G, h0 = g * group + blockIdx.z * kMaxRep, rep = min(kMaxRep, group - blockIdx.z * kMaxRep);
+  const int d = p.d, dv = p.dv, dt = p.dt;
   float* qs = smem;                         // [rep][d], scaled by scale * temp
   float* ps = qs + rep * d;                 // [rep][kDecThreads]
   float* red = ps + rep * kDecThreads;      // [rep][4] warp partials, then [rep] results at red + rep * 4
@@ -231,7 +233,7 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
   const int64_t cbase = ((int64_t)slot * p.G + g) * p.rows;
 
   for (int idx = tid; idx < rep * d; idx += kDecThreads) {
-    const int h = g * rep + idx / d;
+    const int h = h0 + idx / d;
     qs[idx] = ld_any(p.qkvg, dt, base + h * d + idx % d) * (p.scale * (p.temp ? ld_any(p.temp, dt, h) : 1.f));
   }
   // append the new key and normalised value (fp32 statistics; the stored value is what later steps read)
@@ -252,7 +254,7 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
   float m[kMaxRep], l[kMaxRep], acc[kMaxRep][kMaxColsPerThread];
 #pragma unroll
   for (int r = 0; r < kMaxRep; ++r) {
-    if (r < rep && p.sink) { m[r] = ld_any(p.sink, dt, g * rep + r); l[r] = 1.f; } else { m[r] = -INFINITY; l[r] = 0.f; }
+    if (r < rep && p.sink) { m[r] = ld_any(p.sink, dt, h0 + r); l[r] = 1.f; } else { m[r] = -INFINITY; l[r] = 0.f; }
 #pragma unroll
     for (int c = 0; c < kMaxColsPerThread; ++c) acc[r][c] = 0.f;
   }
@@ -291,7 +293,7 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
 #pragma unroll
     for (int r = 0; r < kMaxRep; ++r)
       if (r < rep) {
-        const float slope = p.slope_base >= 0.f ? exp2f(-p.slope_base * (float)(g * rep + r + 1) / (float)p.H) : 0.f;
+        const float slope = p.slope_base >= 0.f ? exp2f(-p.slope_base * (float)(h0 + r + 1) / (float)p.H) : 0.f;
         s[r] = have ? s[r] - slope * (float)(n - j) : -INFINITY;
         const float wm = rb::warp_max(s[r]);
         if (lane == 0) red[r * 4 + warp] = wm;
@@ -338,7 +340,7 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
 #pragma unroll
   for (int r = 0; r < kMaxRep; ++r)
     if (r < rep) {
-      const int h = g * rep + r;
+      const int h = h0 + r;
       float f = l[r] > 0.f ? 1.f / l[r] : 0.f;
       if (p.gate) f *= 1.f / (1.f + expf(-ld_any(p.qkvg, dt, base + og + h)));
 #pragma unroll
@@ -614,12 +616,12 @@ extern "C" int rb_sink_window_decode(const void* qkvg, int64_t ld, void* out, co
                                      const int* lens, const int* slots, int B, int H, int G, int d, int dv, int rows, float scale, int window,
                                      int keep, float slope_base, int gate, int do_norm, float eps, int dt, cudaStream_t s) {
   if (B == 0) return 0;
-  const int rep = H / G;
-  if (H % G || rep > kMaxRep || dv > kDecThreads * kMaxColsPerThread) return -1;
+  const int rep = min(H / G, kMaxRep);
+  if (H % G || dv > kDecThreads * kMaxColsPerThread) return -1;
   DecodeParams p{qkvg, ld, out, temp, sink, kc, vc, lens, slots, H, G, d, dv, rows, window, keep, gate, do_norm, dt, scale, slope_base, eps};
   const size_t smem = sizeof(float) * ((size_t)rep * d + (size_t)rep * kDecThreads + rep * 5 + 32 + dv + kDecThreads);
   if (smem > 48 * 1024) cudaFuncSetAttribute(sink_window_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  sink_window_decode_kernel<<<dim3(B, G), kDecThreads, smem, s>>>(p);
+  sink_window_decode_kernel<<<dim3(B, G, RB_CEIL_DIV(H / G, kMaxRep)), kDecThreads, smem, s>>>(p);
   return 0;
 }
 

@@ -157,7 +157,7 @@ def attn_oracle(a, m, qkvg, temp, sink, lens, eps=1e-5):
 
 
 ATTN_SHAPES = [(4, 2, 8, 16, 5, 2), (1, 1, 16, 16, 1, 0), (3, 3, 6, 5, 7, 9), (2, 1, 32, 24, None, 0), (4, 4, 48, 40, 33, 3),
-               (8, 2, 64, 64, 40, 40), (2, 2, 128, 72, 64, 1)]
+               (8, 2, 64, 64, 40, 40), (2, 2, 128, 72, 64, 1), (20, 1, 8, 12, 6, 1)]
 
 
 @pytest.mark.parametrize("device,dtype", ALL)
