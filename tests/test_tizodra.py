@@ -235,7 +235,7 @@ def test_window_attention_prefill_cache_then_decode(device, dtype, H, G, d, dv, 
 
 
 @pytest.mark.parametrize("device,dtype", ALL)
-@pytest.mark.parametrize("H,G,d,window,keep,S", [(4, 2, 64, None, 0, 1024), (2, 2, 128, 384, 10, 2048), (8, 1, 64, 300, 200, 600)])
+@pytest.mark.parametrize("H,G,d,window,keep,S", [(4, 2, 64, None, 0, 2048), (2, 2, 128, 384, 10, 2048), (8, 1, 64, 300, 200, 600)])
 def test_window_decode_long_context_key_splits(device, dtype, H, G, d, window, keep, S):
     """Contexts of hundreds of keys (the 16-bit decode kernel cuts them into several ranges and merges the partial softmaxes), rings
     that wrap while decoding, unequal rows in one batch."""
