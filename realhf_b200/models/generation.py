@@ -221,6 +221,8 @@ def _final_logits(model: ReaLModel, hidden: torch.Tensor) -> torch.Tensor:
     f8 = model._fp8.get("head") if model._fp8_active and model._fp8 else None
     if f8 is not None and hidden.shape[0] <= 128:
         return f8(hidden)
+    if model.config.logit_scale is not None and model.ctx.tp_size == 1:
+        return OF.linear_f32(hidden, model.head_weight()).mul_(model.config.logit_scale)   # fp32 out of the GEMM, scaled in place
     lg = OF.linear(hidden, model.head_weight())
     if model.ctx.tp_size > 1:
         lg = TP._gather_last_dim(lg, model.ctx)

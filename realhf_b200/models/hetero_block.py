@@ -120,39 +120,72 @@ def _delta_decode(model, i: int, li: int, h: torch.Tensor, k_caches, v_caches, s
 
 def loop_inject(model, i: int, x: torch.Tensor, x0: torch.Tensor) -> torch.Tensor:
     """Start of a pass of the loop: x <- W_in [x; x0] (x0 = the embedding output), back on the residual stream's dtype."""
-    y = OF.linear(OF.concat_cast(x, x0, model.dtype), model.p[f"{i}.loop_in.weight"])
-    return y.to(x.dtype)
+    cat = OF.concat_cast(x, x0, model.dtype)
+    w = model.p[f"{i}.loop_in.weight"]
+    return OF.linear_f32(cat, w) if x.dtype == torch.float32 else OF.linear(cat, w).to(x.dtype)
 
 
-def _finish_block(model, i: int, b, x: torch.Tensor, y: torch.Tensor):
+def plain_prenorm(c) -> bool:
+    """One RMSNorm per sublayer and nothing else around it: a sublayer's residual add can wait for the next norm kernel."""
+    return c.norm_groups == 1 and not c.sandwich_norm and not c.conv_taps
+
+
+def first_norm(model, i: int, x: torch.Tensor, pending: Optional[torch.Tensor]) -> torch.Tensor:
+    """Input of block i's mixer in a plain pre-norm stack; a branch output still owed to the stream is added in the same kernel."""
+    w, eps = model.p[f"{i}.attn.ln.weight"], model.config.layer_norm_epsilon
+    if pending is not None:
+        return OF.add_rms_norm_(x, pending, w, eps, model.dtype)
+    return OF.sublayer_input(x, w, 1, eps, None, None, model.dtype)
+
+
+def settle(model, x: torch.Tensor, pending: Optional[torch.Tensor]) -> torch.Tensor:
+    """Add a branch output that a block left pending (the caller needs the stream itself)."""
+    if pending is not None:
+        OF.residual_add_norm_(x, pending, None, 1, model.config.layer_norm_epsilon)
+    return x
+
+
+def _finish_block(model, i: int, b, x: torch.Tensor, y: torch.Tensor, defer: bool = False) -> Optional[torch.Tensor]:
     """x += mixer output y, then the feed-forward sublayer (same code for packed and one-token batches: neither has a state).  In
-    a plain pre-norm stack the add is fused into the feed-forward's norm."""
+    a plain pre-norm stack the add is fused into the feed-forward's norm, and with `defer` the block's last branch output is
+    returned instead of added: the next block's first norm (or the final norm) adds it."""
     c, p = model.config, model.p
     G, eps = c.norm_groups, c.layer_norm_epsilon
     post = p.get(f"{i}.attn.ln_post.weight")
     if b.mlp is None:
+        if defer and post is None:
+            return y
         OF.residual_add_norm_(x, y, post, G, eps)
-        return
+        return None
     if post is None and G == 1:
         h = OF.add_rms_norm_(x, y, p[f"{i}.mlp.ln.weight"], eps, model.dtype)
     else:
         OF.residual_add_norm_(x, y, post, G, eps)
         h = OF.sublayer_input(x, p[f"{i}.mlp.ln.weight"], G, eps, None, None, model.dtype)
-    OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
+    y2 = _mlp(model, i, h, b.mlp)
+    post2 = p.get(f"{i}.mlp.ln_post.weight")
+    if defer and post2 is None:
+        return y2
+    OF.residual_add_norm_(x, y2, post2, G, eps)
+    return None
 
 
-def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
-    """Block i (1-based layer index; li = index among this stage's block runs) on the packed batch; x [T, H] is updated in place."""
+def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta, pending: Optional[torch.Tensor] = None, defer: bool = False):
+    """Block i (1-based layer index; li = index among this stage's block runs) on the packed batch; x [T, H] is updated in place.
+    Returns (x, pending): `pending` is a branch output not yet added to x (only with `defer`, in plain pre-norm stacks), which the
+    caller hands to the next block (`pending=`) or settles."""
     c, p = model.config, model.p
     b = c.blocks[i - 1]
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
     keep = meta.k is not None
     if b.mixer != "latent_attention":
-        h = OF.sublayer_input(x, p[f"{i}.attn.ln.weight"], G, eps, None, None, model.dtype)
+        defer = defer and plain_prenorm(c)
+        h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G, eps,
+                                                                                       None, None, model.dtype)
         y = _window_attention_packed(model, i, li, h, meta) if b.mixer == "window_attention" else _delta_packed(model, i, li, h, meta)
-        _finish_block(model, i, b, x, y)
-        return x
+        return x, _finish_block(model, i, b, x, y, defer)
+    settle(model, x, pending)
     conv = meta.v[li] if keep and c.conv_taps else None
     h = OF.sublayer_input(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"), meta.pos, model.dtype,
                           conv[0] if conv is not None else None, meta.tok_slot, meta.remain)
@@ -172,24 +205,27 @@ def block_packed(model, i: int, li: int, x: torch.Tensor, meta: PackedMeta) -> t
         h = OF.sublayer_input(x, p[f"{i}.mlp.ln.weight"], G, eps, p.get(f"{i}.mlp.canon.weight"), meta.pos, model.dtype,
                               conv[1] if conv is not None else None, meta.tok_slot, meta.remain)
         OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
-    return x
+    return x, None
 
 
 def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.Tensor], v_caches: List[torch.Tensor],
-                 cache_lens: torch.Tensor, slots: Optional[torch.Tensor]) -> torch.Tensor:
-    """Block i for one new token per row; x [B, H] is updated in place.  Row b lives in state slot slots[b] (None: slot b)."""
+                 cache_lens: torch.Tensor, slots: Optional[torch.Tensor], pending: Optional[torch.Tensor] = None, defer: bool = False):
+    """Block i for one new token per row; x [B, H] is updated in place.  Row b lives in state slot slots[b] (None: slot b).
+    Returns (x, pending) as `block_packed` does."""
     c, p = model.config, model.p
     b = c.blocks[i - 1]
     a = b.attn
     G, eps = c.norm_groups, c.layer_norm_epsilon
     if b.mixer != "latent_attention":
-        h = OF.sublayer_input_step(x, p[f"{i}.attn.ln.weight"], G, eps, None, None, slots, model.dtype)
+        defer = defer and plain_prenorm(c)
+        h = first_norm(model, i, x, pending) if plain_prenorm(c) else OF.sublayer_input_step(settle(model, x, pending), p[f"{i}.attn.ln.weight"], G,
+                                                                                            eps, None, None, slots, model.dtype)
         if b.mixer == "window_attention":
             y = _window_attention_decode(model, i, li, h, k_caches, v_caches, cache_lens, slots)
         else:
             y = _delta_decode(model, i, li, h, k_caches, v_caches, slots)
-        _finish_block(model, i, b, x, y)
-        return x
+        return x, _finish_block(model, i, b, x, y, defer)
+    settle(model, x, pending)
     conv = v_caches[li] if c.conv_taps else None
     h = OF.sublayer_input_step(x, p[f"{i}.attn.ln.weight"], G, eps, p.get(f"{i}.attn.canon.weight"),
                                conv[0] if conv is not None else None, slots, model.dtype)
@@ -202,12 +238,15 @@ def block_decode(model, i: int, li: int, x: torch.Tensor, k_caches: List[torch.T
         h = OF.sublayer_input_step(x, p[f"{i}.mlp.ln.weight"], G, eps, p.get(f"{i}.mlp.canon.weight"),
                                    conv[1] if conv is not None else None, slots, model.dtype)
         OF.residual_add_norm_(x, _mlp(model, i, h, b.mlp), p.get(f"{i}.mlp.ln_post.weight"), G, eps)
-    return x
+    return x, None
 
 
-def final_norm(model, x: torch.Tensor) -> torch.Tensor:
+def final_norm(model, x: torch.Tensor, pending: Optional[torch.Tensor] = None) -> torch.Tensor:
     c = model.config
-    return OF.sublayer_input(x, model.p[f"{c.n_layers}.ln_f.weight"], c.norm_groups, c.layer_norm_epsilon, None, None, model.dtype)
+    w = model.p[f"{c.n_layers}.ln_f.weight"]
+    if pending is not None and plain_prenorm(c):
+        return OF.add_rms_norm_(x, pending, w, c.layer_norm_epsilon, model.dtype)
+    return OF.sublayer_input(settle(model, x, pending), w, c.norm_groups, c.layer_norm_epsilon, None, None, model.dtype)
 
 
 def ring_rows(cfg, block: int, max_len: int) -> int:

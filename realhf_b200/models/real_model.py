@@ -613,16 +613,20 @@ class ReaLModel(nn.Module):
         with torch.no_grad():
             if 0 in self.layers:
                 x = x0 = self._embed(input_ids, meta.pos)
+            pend = None  # a block's last branch output, added by the next norm kernel (plain pre-norm stacks)
             for li, (i, starts_pass) in enumerate(self.local_runs()):
                 if starts_pass and c.loop.inject:
-                    x = HB.loop_inject(self, i, x, x0)
+                    x = HB.loop_inject(self, i, HB.settle(self, x, pend), x0)
+                    pend = None
                 elif x is x0 and c.loop is not None:
                     x = x0.clone()  # the blocks update the stream in place; the loop reads the embedding output again
-                x = HB.block_packed(self, i, li, x, meta)
+                x, pend = HB.block_packed(self, i, li, x, meta, pend, defer=trace is None)
                 if trace is not None:
                     trace.append(x.clone())
             if c.n_layers in self.layers:
-                x = HB.final_norm(self, x)
+                x = HB.final_norm(self, x, pend)
+            else:
+                x = HB.settle(self, x, pend)
         if not self.is_last_stage:
             return x
         return ModelOutput(hidden=x, head_weight=self.head_weight(), ctx=self.ctx, is_critic=c.is_critic, softcap=c.logit_softcap,
@@ -669,15 +673,17 @@ class ReaLModel(nn.Module):
             x = x0 = hidden
             if 0 in self.layers:
                 x = x0 = self._embed(input_ids, cache_lens, slots)   # a new token's position is its slot's length
+            pend = None
             for li, (i, starts_pass) in enumerate(self.local_runs()):
                 if starts_pass and c.loop.inject:
-                    x = HB.loop_inject(self, i, x, x0)
+                    x = HB.loop_inject(self, i, HB.settle(self, x, pend), x0)
+                    pend = None
                 elif x is x0 and c.loop is not None:
                     x = x0.clone()
-                x = HB.block_decode(self, i, li, x, k_caches, v_caches, cache_lens, slots)
+                x, pend = HB.block_decode(self, i, li, x, k_caches, v_caches, cache_lens, slots, pend, defer=True)
             if c.n_layers in self.layers:
-                x = HB.final_norm(self, x)
-            return x
+                return HB.final_norm(self, x, pend)
+            return HB.settle(self, x, pend)
         assert slots is None, "slot indirection is a feature of heterogeneous stacks"
         nq, nkv = self._local_heads()
         hd = c.head_dim

@@ -10,6 +10,8 @@
 //                    preceding rows (pos[t] tells how many belong to the sequence), and the last taps - 1 raw inputs of every
 //                    sequence go to conv_state [n_slots, taps - 1, C] (oldest first).  Step form (pos == null): earlier inputs
 //                    come from conv_state[slot], which is shifted by one.
+// Kernels on the decode path are launched with programmatic dependent launch (they signal their successors at once and wait for
+// their predecessor before the first global access), like the framework's other decode kernels.
 //   delta_rule       the recurrence.  A column of S depends only on its own v column, so columns are independent: a thread group of
 //                    LPC lanes owns one column (lane l holds rows e * LPC + l, 32 registers each), a CTA 128 / LPC columns of one
 //                    (sequence, head).  q, k, v, beta, g of 8 tokens at a time are staged in shared memory.  Packed form: S starts
@@ -24,28 +26,48 @@ using rb::st_any;
 
 constexpr int kMaxTaps = 8;
 
-__global__ void __launch_bounds__(256) delta_prepare_kernel(const void* __restrict__ proj, int64_t ld, int dt, const void* __restrict__ conv_w,
+// One CTA per (token, unit); a unit is a q or k head, a v head, or the 2H gate scalars (as in the tiled kernel below), so that a
+// decode batch of a few rows still spreads over the GPU.
+__global__ void __launch_bounds__(128) delta_prepare_kernel(const void* __restrict__ proj, int64_t ld, int dt, const void* __restrict__ conv_w,
                                                             const void* __restrict__ A_log, const void* __restrict__ dt_bias,
                                                             float* __restrict__ u, const int* __restrict__ pos, float* __restrict__ conv_state,
                                                             const int* __restrict__ tok_slot, const int* __restrict__ remain,
                                                             const int* __restrict__ slots, int H, int G, int d, int dv, int taps,
                                                             float unit_eps) {
-  extern __shared__ float ys[];               // [C] convolved + SiLU
+  extern __shared__ float ys[];               // [channels of the unit] convolved + SiLU
+  __shared__ float red[32];
   const int64_t t = blockIdx.x;
+  const int unit = blockIdx.y;
   const int nqk = G * d, nv = H * dv, C = 2 * nqk + nv, UW = C + 2 * H;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  rb::pdl_trigger();
+  rb::pdl_wait();
+  if (unit == 2 * G + H) {
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+      const float b = ld_any(proj, dt, t * ld + C + nv + h);
+      u[t * UW + C + h] = 1.f / (1.f + expf(-b));
+      const float a = ld_any(proj, dt, t * ld + C + nv + H + h) + ld_any(dt_bias, dt, h);
+      const float sp = a > 20.f ? a : log1pf(expf(a));
+      u[t * UW + C + H + h] = expf(-expf(ld_any(A_log, dt, h)) * sp);
+    }
+    return;
+  }
+  const bool is_qk = unit < 2 * G;
+  const int us = is_qk ? d : dv;
+  const int c_base = is_qk ? unit * d : 2 * nqk + (unit - 2 * G) * dv;
   const bool step = pos == nullptr;
   const int p = step ? 0 : pos[t];
   int slot = -1;
   if (conv_state != nullptr) slot = step ? (slots ? slots[t] : (int)t) : tok_slot[t];
   const int rem = (!step && conv_state != nullptr) ? remain[t] : 0;
   float* st = (slot >= 0 && taps > 1) ? conv_state + (int64_t)slot * (taps - 1) * C : nullptr;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  float ss = 0.f;
+  for (int cl = threadIdx.x; cl < us; cl += blockDim.x) {
+    const int c = c_base + cl;
     const float x = ld_any(proj, dt, t * ld + c);
-    float y = x * ld_any(conv_w, dt, (int64_t)c * taps + taps - 1);
     float hist[kMaxTaps - 1];
+    float y = 0.f;
 #pragma unroll
-    for (int back = 1; back < kMaxTaps; ++back) {
+    for (int back = kMaxTaps - 1; back >= 1; --back) {       // oldest first, the current token last: the tiled kernel's order
       if (back < taps) {
         float xb;
         if (step) xb = st ? st[(int64_t)(taps - 1 - back) * C + c] : 0.f;
@@ -54,6 +76,7 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const void* __restri
         y = fmaf(xb, ld_any(conv_w, dt, (int64_t)c * taps + taps - 1 - back), y);
       }
     }
+    y = fmaf(x, ld_any(conv_w, dt, (int64_t)c * taps + taps - 1), y);
     if (st != nullptr) {
       if (step) {           // shift: row i <- row i + 1, the newest row <- x (this thread owns channel c of the slot)
 #pragma unroll
@@ -63,26 +86,17 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const void* __restri
         st[(int64_t)(taps - 2 - rem) * C + c] = x;
       }
     }
-    ys[c] = y / (1.f + expf(-y));
+    y = y / (1.f + expf(-y));
+    ys[cl] = y;
+    ss = fmaf(y, y, ss);
   }
-  __syncthreads();
-  // unit norms of the 2 G heads of q and k: one warp per head, fixed order
-  for (int hd = warp; hd < 2 * G; hd += nwarp) {
-    float ss = 0.f;
-    for (int e = lane; e < d; e += 32) { const float v = ys[hd * d + e]; ss += v * v; }
-    ss = rb::warp_sum(ss);
-    float r = 1.f / sqrtf(ss + unit_eps);
-    if (hd < G) r *= 1.f / sqrtf((float)d);
-    for (int e = lane; e < d; e += 32) u[t * UW + hd * d + e] = ys[hd * d + e] * r;
+  float r = 1.f;
+  if (is_qk) {
+    ss = rb::block_reduce<false>(ss, red);
+    r = 1.f / sqrtf(ss + unit_eps);
+    if (unit < G) r *= 1.f / sqrtf((float)d);
   }
-  for (int c = 2 * nqk + threadIdx.x; c < C; c += blockDim.x) u[t * UW + c] = ys[c];
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    const float b = ld_any(proj, dt, t * ld + C + nv + h);
-    u[t * UW + C + h] = 1.f / (1.f + expf(-b));
-    const float a = ld_any(proj, dt, t * ld + C + nv + H + h) + ld_any(dt_bias, dt, h);
-    const float sp = a > 20.f ? a : log1pf(expf(a));
-    u[t * UW + C + H + h] = expf(-expf(ld_any(A_log, dt, h)) * sp);
-  }
+  for (int cl = threadIdx.x; cl < us; cl += blockDim.x) u[t * UW + c_base + cl] = ys[cl] * r;   // a thread re-reads its own entries
 }
 
 // Packed form for long batches: a CTA owns 16 consecutive tokens x one unit of channels (a q or k head, a v head, or the 2H gate
@@ -216,6 +230,8 @@ __global__ void __launch_bounds__(kScanThreads, 3) delta_rule_kernel(ScanParams 
   const int tid = threadIdx.x, l = tid % LPC, col = c0 + tid / LPC;
   const bool active = col < dv;
   int t0, t1;
+  rb::pdl_trigger();
+  rb::pdl_wait();
   if (p.step) { t0 = seq; t1 = seq + 1; } else { t0 = p.cu[seq]; t1 = p.cu[seq + 1]; }
   if (t1 <= t0) return;
   const int slot = p.s_state == nullptr ? -1 : (p.slots ? p.slots[seq] : (p.step ? seq : -1));
@@ -315,6 +331,8 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
                                                               const void* __restrict__ gate, int64_t ldg, int dtg, void* __restrict__ out, int dto,
                                                               int64_t rows, int H, int dv, float eps) {
   const int64_t r = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  rb::pdl_trigger();
+  rb::pdl_wait();
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
   const int64_t t = r / H;
@@ -348,11 +366,11 @@ extern "C" int rb_delta_prepare(const void* proj, int64_t ld, int dt, const void
                                                                dv, taps, unit_eps);
     return 0;
   }
-  const size_t smem = sizeof(float) * (size_t)C;
-  if (smem > 200 * 1024) return -2;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  delta_prepare_kernel<<<(unsigned)T, 256, smem, s>>>(proj, ld, dt, conv_w, A_log, dt_bias, u, pos, conv_state, tok_slot, remain, slots, H, G, d, dv,
-                                                      taps, unit_eps);
+  const size_t smem = sizeof(float) * (size_t)(d > dv ? d : dv);
+  if (smem > 48 * 1024) return -2;
+  if (rb::launch_pdl(delta_prepare_kernel, dim3((unsigned)T, 2 * G + H + 1), dim3(128), smem, s, proj, ld, dt, conv_w, A_log, dt_bias, u, pos,
+                     conv_state, tok_slot, remain, slots, H, G, d, dv, taps, unit_eps) != cudaSuccess)
+    return -3;
   return 0;
 }
 
@@ -365,19 +383,20 @@ extern "C" int rb_delta_rule(const float* u, float* o, const int* cu, float* s_s
   ScanParams p{u, o, cu, s_state, slots, H, G, d, dv, step};
   const size_t smem = 2 * sizeof(float) * ((size_t)2 * kTok * kEPL * lpc + (size_t)kTok * ncol + 2 * kTok);   // two staging buffers
   dim3 grid(n_seqs, H, RB_CEIL_DIV(dv, ncol));
+  cudaError_t e;
   switch (lpc) {
-    case 1: delta_rule_kernel<1><<<grid, kScanThreads, smem, s>>>(p); break;
-    case 2: delta_rule_kernel<2><<<grid, kScanThreads, smem, s>>>(p); break;
-    case 4: delta_rule_kernel<4><<<grid, kScanThreads, smem, s>>>(p); break;
-    default: delta_rule_kernel<8><<<grid, kScanThreads, smem, s>>>(p); break;
+    case 1: e = rb::launch_pdl(delta_rule_kernel<1>, grid, dim3(kScanThreads), smem, s, p); break;
+    case 2: e = rb::launch_pdl(delta_rule_kernel<2>, grid, dim3(kScanThreads), smem, s, p); break;
+    case 4: e = rb::launch_pdl(delta_rule_kernel<4>, grid, dim3(kScanThreads), smem, s, p); break;
+    default: e = rb::launch_pdl(delta_rule_kernel<8>, grid, dim3(kScanThreads), smem, s, p); break;
   }
-  return 0;
+  return e == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int rb_gated_head_norm(const float* o, const void* w, int dtw, const void* gate, int64_t ldg, int dtg, void* out, int dto, int64_t T, int H,
                                   int dv, float eps, cudaStream_t s) {
   const int64_t rows = T * H;
   if (rows == 0) return 0;
-  gated_head_norm_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(o, w, dtw, gate, ldg, dtg, out, dto, rows, H, dv, eps);
-  return 0;
+  return rb::launch_pdl(gated_head_norm_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, s, o, w, dtw, gate, ldg, dtg, out, dto, rows, H, dv,
+                        eps) == cudaSuccess ? 0 : -3;
 }

@@ -12,6 +12,8 @@ namespace {
 __global__ void embed_sinusoid_kernel(const int64_t* __restrict__ ids, const void* __restrict__ wte, int dtw, const int* __restrict__ pos,
                                       const int* __restrict__ slots, const float* __restrict__ inv_freq, float* __restrict__ out, int W, int vocab) {
   const int64_t t = blockIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
   int64_t id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
   const float p = (float)(slots ? pos[slots[t]] : pos[t]);
@@ -32,6 +34,8 @@ __global__ void concat_cast_kernel(const void* __restrict__ a, int dta, int Wa, 
                                    int dto) {
   const int64_t t = blockIdx.x;
   const int W = Wa + Wb;
+  rb::pdl_trigger();
+  rb::pdl_wait();
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float v = i < Wa ? rb::ld_any(a, dta, t * Wa + i) : rb::ld_any(b, dtb, t * Wb + (i - Wa));
     rb::st_any(out, dto, t * W + i, v);
@@ -40,6 +44,8 @@ __global__ void concat_cast_kernel(const void* __restrict__ a, int dta, int Wa, 
 
 __global__ void relu2_kernel(const void* __restrict__ x, void* __restrict__ out, int dt, int64_t n) {
   const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  rb::pdl_trigger();
+  rb::pdl_wait();
   if (i0 + 3 < n) {
     float4 v = rb::ld4_any(x, dt, i0);
     v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
@@ -56,6 +62,8 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(void* __restrict__ x
   const int64_t base = (int64_t)blockIdx.x * W;
   const bool vec = (W & 3) == 0;
   float ss = 0.f;
+  rb::pdl_trigger();
+  rb::pdl_wait();
   if (vec) {
     for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
       float4 v = rb::ld4_any(x, dtx, base + i);
@@ -92,26 +100,22 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(void* __restrict__ x
 extern "C" int rb_rms_norm_rows(void* x, int dtx, const void* y, int dty, const void* w, int dtw, void* out, int dto, int64_t rows, int W, float eps,
                                 cudaStream_t s) {
   if (rows == 0) return 0;
-  rms_norm_rows_kernel<<<(unsigned)rows, 256, 0, s>>>(x, dtx, y, dty, w, dtw, out, dto, W, eps);
-  return 0;
+  return rb::launch_pdl(rms_norm_rows_kernel, dim3((unsigned)rows), dim3(256), 0, s, x, dtx, y, dty, w, dtw, out, dto, W, eps) == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int rb_embed_sinusoid(const int64_t* ids, const void* wte, int dtw, const int* pos, const int* slots, const float* inv_freq, float* out,
                                  int64_t T, int W, int vocab, cudaStream_t s) {
   if (T == 0) return 0;
-  embed_sinusoid_kernel<<<(unsigned)T, 128, 0, s>>>(ids, wte, dtw, pos, slots, inv_freq, out, W, vocab);
-  return 0;
+  return rb::launch_pdl(embed_sinusoid_kernel, dim3((unsigned)T), dim3(128), 0, s, ids, wte, dtw, pos, slots, inv_freq, out, W, vocab) == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int rb_concat_cast(const void* a, int dta, int Wa, const void* b, int dtb, int Wb, void* out, int dto, int64_t T, cudaStream_t s) {
   if (T == 0) return 0;
-  concat_cast_kernel<<<(unsigned)T, 256, 0, s>>>(a, dta, Wa, b, dtb, Wb, out, dto);
-  return 0;
+  return rb::launch_pdl(concat_cast_kernel, dim3((unsigned)T), dim3(256), 0, s, a, dta, Wa, b, dtb, Wb, out, dto) == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int rb_relu2(const void* x, void* out, int dt, int64_t n, cudaStream_t s) {
   if (n == 0) return 0;
   const int64_t blocks = (n + 1023) / 1024;
-  relu2_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, out, dt, n);
-  return 0;
+  return rb::launch_pdl(relu2_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, out, dt, n) == cudaSuccess ? 0 : -3;
 }

@@ -354,7 +354,9 @@ __global__ void __launch_bounds__(kDecThreads) sink_window_decode_kernel(DecodeP
 // ------------------------------------------------------------------------------------------------ decode, 16-bit fast path
 // Equal query / value head size HD of 64 or 128, 16-bit storage: the streaming design of the dense-cache decode kernel
 // (attn_decode.cu).  A group of HD / 8 lanes owns one cache row at a time with 16-byte loads, REP query heads share every load,
-// the loop is unrolled x4, and the visible keys are cut into `splits` ranges (grid.z) whose partial (max, sum, acc) are merged
+// the loop is unrolled x4, the softmax exponentials use the fast intrinsic (fp32 arithmetic; the all-fp32 kernel above keeps expf),
+// launches are programmatic dependent launches like the dense kernel's, and the visible keys are cut into `splits` ranges (grid.z)
+// whose partial (max, sum, acc) are merged
 // by a second kernel, so that a batch of few rows still fills the GPU.  The visible keys are indexed 0 .. nk - 1 (kept first
 // tokens, then the window); index -> cache row needs no division (the ring wraps at most once inside a window).
 constexpr int kFastWarps = 4, kFastThreads = kFastWarps * 32;
@@ -384,6 +386,8 @@ __global__ void __launch_bounds__(kFastThreads) sink_window_decode_fast_kernel(F
   constexpr int LPR = HD / 8, RPW = 32 / LPR;
   const int b = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane % LPR, rsel = lane / LPR;
+  rb::pdl_trigger();
+  rb::pdl_wait();
   const int slot = p.slots ? p.slots[b] : b;
   const int n = p.lens[slot];
   const T* row_in = reinterpret_cast<const T*>(p.qkvg) + (int64_t)b * p.ld;
@@ -456,7 +460,7 @@ __global__ void __launch_bounds__(kFastThreads) sink_window_decode_fast_kernel(F
       for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(gmask, s, o, LPR);
       s -= slope[r] * dist;
       const float mn = fmaxf(m[r], s);
-      const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mn), pr = expf(s - mn);
+      const float corr = (m[r] == -INFINITY) ? 0.f : __expf(m[r] - mn), pr = __expf(s - mn);
       l[r] = l[r] * corr + pr;
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[r][i] = fmaf(acc[r][i], corr, pr * vf[i]);
@@ -498,7 +502,7 @@ __global__ void __launch_bounds__(kFastThreads) sink_window_decode_fast_kernel(F
     for (int o = LPR; o < 32; o <<= 1) {
       const float m2 = __shfl_xor_sync(0xffffffffu, m[r], o), l2 = __shfl_xor_sync(0xffffffffu, l[r], o);
       const float mn = fmaxf(m[r], m2);
-      const float c1 = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mn), c2 = (m2 == -INFINITY) ? 0.f : expf(m2 - mn);
+      const float c1 = (m[r] == -INFINITY) ? 0.f : __expf(m[r] - mn), c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
       l[r] = l[r] * c1 + l2 * c2;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -522,7 +526,7 @@ __global__ void __launch_bounds__(kFastThreads) sink_window_decode_fast_kernel(F
     float lg = 0.f, ag = 0.f;
 #pragma unroll
     for (int w = 0; w < kFastWarps; ++w) {
-      const float cf = (sm_m[w][r] == -INFINITY) ? 0.f : expf(sm_m[w][r] - mg);
+      const float cf = (sm_m[w][r] == -INFINITY) ? 0.f : __expf(sm_m[w][r] - mg);
       lg += sm_l[w][r] * cf;
       ag += sm_acc[w][r][c] * cf;
     }
@@ -544,6 +548,8 @@ __global__ void sink_window_decode_merge_kernel(const float* __restrict__ part_a
                                                 int64_t ld, int og, int H, int gate, T* __restrict__ out, int splits) {
   const int64_t bh = blockIdx.x;
   const int c = threadIdx.x;
+  rb::pdl_trigger();
+  rb::pdl_wait();
   float mg = -INFINITY;
   for (int s = 0; s < splits; ++s) mg = fmaxf(mg, part_ml[(bh * splits + s) * 2]);
   float lg = 0.f, ag = 0.f;
@@ -562,7 +568,7 @@ template <typename T, int HD>
 int launch_fast(const FastParams& fp, int B, cudaStream_t s) {
   const DecodeParams& p = fp.d;
   dim3 grid(B, p.G, fp.splits);
-#define RB_L(REP) sink_window_decode_fast_kernel<T, HD, REP><<<grid, kFastThreads, 0, s>>>(fp)
+#define RB_L(REP) rb::launch_pdl(sink_window_decode_fast_kernel<T, HD, REP>, grid, dim3(kFastThreads), 0, s, fp)
   switch (p.H / p.G) {
     case 1: RB_L(1); break;
     case 2: RB_L(2); break;
@@ -572,8 +578,8 @@ int launch_fast(const FastParams& fp, int B, cudaStream_t s) {
   }
 #undef RB_L
   if (fp.splits > 1)
-    sink_window_decode_merge_kernel<T, HD><<<B * p.H, HD, 0, s>>>(fp.part_acc, fp.part_ml, reinterpret_cast<const T*>(p.qkvg), p.ld,
-                                                                  p.H * HD + 2 * p.G * HD, p.H, p.gate, reinterpret_cast<T*>(p.out), fp.splits);
+    rb::launch_pdl(sink_window_decode_merge_kernel<T, HD>, dim3(B * p.H), dim3(HD), 0, s, (const float*)fp.part_acc, (const float*)fp.part_ml,
+                   reinterpret_cast<const T*>(p.qkvg), p.ld, p.H * HD + 2 * p.G * HD, p.H, p.gate, reinterpret_cast<T*>(p.out), fp.splits);
   return 0;
 }
 

@@ -455,6 +455,19 @@ def linear(x, w, bias=None):
     return F.linear(x, w, bias)
 
 
+def linear_f32(x, w):
+    """fp32 y = x @ w.T from operands of the model dtype: 16-bit CUDA operands keep the fp32 accumulator of the tcgen05 GEMM as the
+    output (no rounding to 16 bit and no separate cast); everything else is the library product, cast."""
+    if x.is_cuda and gemm_impl() is not None and x.dtype in (torch.bfloat16, torch.float16):
+        from realhf_b200.ops import gemm as G
+        x2 = x.reshape(-1, x.shape[-1])
+        if gemm_impl() is G.linear and G.supported(x2, w):
+            if x2.stride(-1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+                x2 = x2.contiguous()
+            return G.gemm(x2, w, out_dtype=torch.float32).view(*x.shape[:-1], w.shape[0])
+    return F.linear(x, w).float()
+
+
 # ------------------------------------------------------------------------------------------------ optimizer
 
 
