@@ -13,7 +13,7 @@
 // Kernels on the decode path are launched with programmatic dependent launch (they signal their successors at once and wait for
 // their predecessor before the first global access), like the framework's other decode kernels.
 //   delta_rule       the recurrence.  A column of S depends only on its own v column, so columns are independent: a thread group of
-//                    LPC lanes owns one column (lane l holds rows e * LPC + l, 32 registers each), a CTA 128 / LPC columns of one
+//                    LPC lanes owns one column (32 or 64 state rows per lane in registers), a CTA 128 / LPC columns of one
 //                    (sequence, head).  q, k, v, beta, g of 8 tokens at a time are staged in shared memory.  Packed form: S starts
 //                    at zero and the final S goes to s_state[slot]; step form: S is loaded from and stored to s_state[slot].
 //   gated_head_norm  o / sqrt(mean(o^2) + eps) * w * silu(gate) per (token, head) -> model type.
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(kPThreads) delta_prepare_tiled_kernel(const vo
 }
 
 // ------------------------------------------------------------------------------------------------ recurrence
-constexpr int kScanThreads = 128, kEPL = 32, kTok = 8;
+constexpr int kScanThreads = 128, kTok = 8;   // kEPL (template): state rows per lane, 32 or 64
 
 struct ScanParams {
   const float* u; float* o;
@@ -220,8 +220,8 @@ struct ScanParams {
 // Row mapping: lane l of a column's LPC lanes holds the state rows ((e / 4) * LPC + l) * 4 + e % 4, e = 0 .. 31, so that its q / k
 // operands are 8 aligned float4 reads of shared memory per token (the lanes of a column read neighbouring float4s, the columns of
 // a warp the same ones).  Dot products run on four independent accumulators.
-template <int LPC>
-__global__ void __launch_bounds__(kScanThreads, 3) delta_rule_kernel(ScanParams p) {
+template <int LPC, int kEPL>
+__global__ void __launch_bounds__(kScanThreads, kEPL == 32 ? 3 : 2) delta_rule_kernel(ScanParams p) {
   constexpr int NCOL = kScanThreads / LPC;
   extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * NCOL;
@@ -377,18 +377,23 @@ extern "C" int rb_delta_prepare(const void* proj, int64_t ld, int dt, const void
 extern "C" int rb_delta_rule(const float* u, float* o, const int* cu, float* s_state, const int* slots, int n_seqs, int H, int G, int d, int dv,
                              int step, cudaStream_t s) {
   if (n_seqs == 0) return 0;
-  if (d > 8 * kEPL || H % G) return -1;
-  const int lpc = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8;
+  if (d > 512 || H % G) return -1;
+  // (lanes per column, state rows per lane): 64 rows per lane from head size 128 up halves the shuffle rounds and the shared
+  // reads per FMA at two CTAs per SM
+  const int lpc = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 2 : d <= 256 ? 4 : 8;
+  const int epl = d <= 64 ? 32 : 64;
   const int ncol = kScanThreads / lpc;
   ScanParams p{u, o, cu, s_state, slots, H, G, d, dv, step};
-  const size_t smem = 2 * sizeof(float) * ((size_t)2 * kTok * kEPL * lpc + (size_t)kTok * ncol + 2 * kTok);   // two staging buffers
+  const size_t smem = 2 * sizeof(float) * ((size_t)2 * kTok * epl * lpc + (size_t)kTok * ncol + 2 * kTok);   // two staging buffers
   dim3 grid(n_seqs, H, RB_CEIL_DIV(dv, ncol));
   cudaError_t e;
-  switch (lpc) {
-    case 1: e = rb::launch_pdl(delta_rule_kernel<1>, grid, dim3(kScanThreads), smem, s, p); break;
-    case 2: e = rb::launch_pdl(delta_rule_kernel<2>, grid, dim3(kScanThreads), smem, s, p); break;
-    case 4: e = rb::launch_pdl(delta_rule_kernel<4>, grid, dim3(kScanThreads), smem, s, p); break;
-    default: e = rb::launch_pdl(delta_rule_kernel<8>, grid, dim3(kScanThreads), smem, s, p); break;
+  if (epl == 32) {
+    if (lpc == 1) e = rb::launch_pdl(delta_rule_kernel<1, 32>, grid, dim3(kScanThreads), smem, s, p);
+    else e = rb::launch_pdl(delta_rule_kernel<2, 32>, grid, dim3(kScanThreads), smem, s, p);
+  } else {
+    if (lpc == 2) e = rb::launch_pdl(delta_rule_kernel<2, 64>, grid, dim3(kScanThreads), smem, s, p);
+    else if (lpc == 4) e = rb::launch_pdl(delta_rule_kernel<4, 64>, grid, dim3(kScanThreads), smem, s, p);
+    else e = rb::launch_pdl(delta_rule_kernel<8, 64>, grid, dim3(kScanThreads), smem, s, p);
   }
   return e == cudaSuccess ? 0 : -3;
 }

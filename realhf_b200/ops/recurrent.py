@@ -130,7 +130,7 @@ def delta_rule_scan_ref(u, d, cu_seqlens, s_state, slots):
 def delta_rule_scan(u, d, cu_seqlens, s_state=None, slots=None):
     """u [T, C + 2H] fp32 (see `delta_prepare`), sequences given by cu_seqlens, each from S = 0.  Returns o [T, H, dv] fp32; with
     `s_state` and `slots` [n_seqs] int32, sequence b's final state is left in s_state[slots[b]] (slots[b] < 0: dropped)."""
-    if use_native(u) and d.qk_dim <= 256:
+    if use_native(u) and d.qk_dim <= 512:
         o = torch.empty(u.shape[0], d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
         lib().delta_rule_scan(u, o, cu_seqlens, s_state, slots if s_state is not None else None, d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim)
         return o
@@ -150,7 +150,7 @@ def delta_rule_step_ref(u, d, s_state, slots):
 
 def delta_rule_step(u, d, s_state, slots):
     """One token per row: s_state[slots[b]] (slots None: row b is slot b) is updated in place.  Returns o [B, H, dv] fp32."""
-    if use_native(u) and d.qk_dim <= 256:
+    if use_native(u) and d.qk_dim <= 512:
         o = torch.empty(u.shape[0], d.n_heads, d.v_dim, dtype=torch.float32, device=u.device)
         lib().delta_rule_step(u, o, s_state, slots, d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim)
         return o
