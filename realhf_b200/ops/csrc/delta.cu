@@ -393,7 +393,10 @@ extern "C" int rb_delta_rule(const float* u, float* o, const int* cu, float* s_s
   } else {
     if (lpc == 2) e = rb::launch_pdl(delta_rule_kernel<2, 64>, grid, dim3(kScanThreads), smem, s, p);
     else if (lpc == 4) e = rb::launch_pdl(delta_rule_kernel<4, 64>, grid, dim3(kScanThreads), smem, s, p);
-    else e = rb::launch_pdl(delta_rule_kernel<8, 64>, grid, dim3(kScanThreads), smem, s, p);
+    else {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(delta_rule_kernel<8, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      e = rb::launch_pdl(delta_rule_kernel<8, 64>, grid, dim3(kScanThreads), smem, s, p);
+    }
   }
   return e == cudaSuccess ? 0 : -3;
 }

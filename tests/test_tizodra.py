@@ -353,7 +353,7 @@ def delta_oracle_inputs(dl, proj, conv_w, A_log, dt_bias, lens):
     return out
 
 
-DELTA_SHAPES = [(4, 2, 8, 16, 4), (1, 1, 32, 32, 1), (2, 2, 48, 24, 2), (3, 1, 64, 40, 3), (2, 1, 128, 136, 4), (1, 1, 160, 8, 5)]
+DELTA_SHAPES = [(4, 2, 8, 16, 4), (1, 1, 32, 32, 1), (2, 2, 48, 24, 2), (3, 1, 64, 40, 3), (2, 1, 128, 136, 4), (1, 1, 160, 8, 5), (1, 1, 272, 16, 2)]
 
 
 @pytest.mark.parametrize("device,dtype", ALL)
