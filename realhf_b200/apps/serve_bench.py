@@ -49,7 +49,7 @@ def tizodra_config(s: dict, n_layers: int = 4) -> dict:
     dlt = dict(type="delta", mixer=dict(conv=s["conv"], dim=s["dim"], heads=s["heads"], kv_heads=s["kv_heads"], vdim=s["vdim"]),
                mlp=dict(kind="dense", ff=s["ff"]))
     layers = [dlt if i in (0, n_layers - 1) else att for i in range(n_layers)]
-    return dict(architecture="Tizodra", layers=layers, logit_scale=0.5, loop=dict(start=1, stop=max(2, n_layers - 1), times=1),
+    return dict(architecture="Tizodra", layers=layers, logit_scale=0.7, loop=dict(start=1, stop=max(2, n_layers - 1), times=1),
                 norm=dict(eps=1e-5), vocab=s["vocab"], width=s["width"])
 
 

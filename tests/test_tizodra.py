@@ -490,7 +490,7 @@ def with_mlp(layer, mlp):
 CONFIGS = {
     # a looped pair in the middle, delta first and last
     "mixed": lambda: dict(architecture="Tizodra", layers=[dlt(), att(), with_mlp(dlt(conv=2), dict(kind="dense", ff=40)), att(), dlt()],
-                          logit_scale=0.25, loop=dict(start=1, stop=3, times=3), norm=dict(eps=1e-5), vocab=96, width=32),
+                          logit_scale=0.25, loop=dict(start=1, stop=3, times=2), norm=dict(eps=1e-5), vocab=96, width=32),
     # every count that can be 1 is 1; the loop covers the whole stack once
     "ones": lambda: dict(architecture="Tizodra", layers=[
         att(dim=4, heads=1, kv_heads=1, vdim=4, mask=dict(size=1, keep_first=0)),
